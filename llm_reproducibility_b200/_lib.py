@@ -1,0 +1,62 @@
+"""ctypes binding of libtbik_b200.so.
+
+There is no CPU fallback: if the library is missing or a call fails, a `RuntimeError`
+is raised with the library's own message.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "libtbik_b200.so")
+
+TBIK_OK = 0
+DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = 0, 1, 2
+NODE_INPUT, NODE_FP32 = 0, 1
+
+_lib: Optional[ctypes.CDLL] = None
+
+_i32, _i64, _vp, _sz = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_size_t
+
+_PROTOTYPES = {
+    "tbik_last_error": (ctypes.c_char_p, []),
+    "tbik_version": (_i32, []),
+    "tbik_tree_shape": (_i32, [_i64, _i32, ctypes.POINTER(_i32), ctypes.POINTER(_i32), ctypes.POINTER(_i32)]),
+    "tbik_gemm": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
+    "tbik_gemm_ex": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _vp]),
+    "tbik_gemm_status": (_i32, [ctypes.POINTER(ctypes.c_uint32)]),
+}
+
+
+def exported_symbols():
+    """Names this binding expects the library to export (kept equal to include/tbik.h)."""
+    return sorted(_PROTOTYPES)
+
+
+def lib() -> ctypes.CDLL:
+    """Load the library once.  torch must be imported first so that its libcudart is the one in use."""
+    global _lib
+    if _lib is None:
+        if not os.path.isfile(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m llm_reproducibility_b200._build` "
+                "(there is no fallback implementation)")
+        import torch  # noqa: F401  (loads libcudart.so.12 into the process)
+        handle = ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL)
+        for name, (res, args) in _PROTOTYPES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def last_error() -> str:
+    return lib().tbik_last_error().decode("utf-8", "replace")
+
+
+def check(rc: int, what: str) -> None:
+    if rc != TBIK_OK:
+        raise RuntimeError(f"{what} failed ({rc}): {last_error()}")

@@ -1,0 +1,560 @@
+// Cross-GPU all-reduce over CUDA-IPC mapped buffers (NVLink 5 / NVSwitch peer loads), no NCCL.
+//
+// tree mode   out[i] = ((x0+x1)+(x2+x3)) + ((x4+x5)+(x6+x7)), every add rounded to the element
+//             type: the rank-pair tree that finishes the K-reduction tree of the row-split GEMM
+//             (reference: custom_tree_all_reduce / packed_tree_reduce,
+//              mini_allreduce/tbik_kernel/csrc/allreduce/custom_all_reduce.cuh:203-234, 301-312).
+// linear mode out[i] = downcast(fp32(x0) + fp32(x1) + ... ) in rank order
+//             (reference: cross_device_reduce_1stage / _2stage, same file :193-201, 236-299).
+//
+// Two schedules, same arithmetic per element so the bits do not depend on the schedule:
+//   one-shot  every GPU loads all n buffers and reduces everything            (latency bound sizes)
+//   two-shot  GPU r reduces the r-th 1/n of the packs into its scratch area, a fenced barrier,
+//             then every GPU gathers the n reduced parts                      (bandwidth bound sizes)
+//
+// Synchronisation is a per-block epoch barrier: block b of rank r stores its epoch into slot
+// [b][r] of every peer's flag array and waits until each of its own slots has reached the epoch
+// (wrap-safe signed compare, so one flag array serves consecutive barriers).  Every wait is
+// bounded: when it runs out the kernel writes a record to a host-visible status word, skips the
+// data phase and returns, so a missing peer can never hang the GPU.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "tbik_internal.h"
+
+namespace tbik {
+
+constexpr int kMaxRanks = 8;
+constexpr int kMaxBlocks = 160;
+constexpr int kThreads = 512;
+constexpr uint64_t kArWaitLimitNs = 2000000000ull;  // default bound of one barrier wait
+
+struct alignas(128) Signal {
+  uint32_t epoch[kMaxBlocks][kMaxRanks];  // private to the owning rank: last epoch used by (block, thread)
+  uint32_t flag[kMaxBlocks][kMaxRanks];   // written by peers: flag[b][r] = last epoch announced by rank r, block b
+};
+
+struct alignas(16) RankData {
+  const void* ptrs[kMaxRanks];
+};
+
+struct RankSignals {
+  Signal* sig[kMaxRanks];
+};
+
+// status record (host-mapped): [0] code (0 ok, 1 barrier timeout) [1] rank [2] block [3] peer
+//                              [4] expected epoch [5] seen value [6] which barrier (1 start, 2 middle, 3 end)
+struct ArStatus {
+  uint32_t w[8];
+};
+
+__device__ __forceinline__ uint64_t ar_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void st_flag_release(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_flag_acquire(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_pack(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+// Per-block barrier across `NG` ranks.  Returns false (for every thread of the block) if a wait
+// ran out.  `which` only labels the status record.
+template <int NG>
+__device__ __forceinline__ bool block_barrier(const RankSignals& sg, Signal* self, int rank, ArStatus* status,
+                                              uint64_t limit_ns, int which, uint32_t* smem_fail) {
+  __syncthreads();  // all data accesses of the previous phase are done (and ordered before the release below)
+  if (threadIdx.x < NG) {
+    const int peer = threadIdx.x;
+    const uint32_t e = self->epoch[blockIdx.x][peer] + 1u;
+    self->epoch[blockIdx.x][peer] = e;
+    st_flag_release(&sg.sig[peer]->flag[blockIdx.x][rank], e);
+    const uint32_t* mine = &self->flag[blockIdx.x][peer];
+    uint32_t seen = ld_flag_acquire(mine);
+    if (static_cast<int32_t>(seen - e) < 0) {
+      const uint64_t t0 = ar_timer_ns();
+      uint32_t it = 0;
+      while (true) {
+        seen = ld_flag_acquire(mine);
+        if (static_cast<int32_t>(seen - e) >= 0) break;
+        if ((++it & 255u) == 0u && ar_timer_ns() - t0 > limit_ns) {
+          if (atomicCAS(&status->w[0], 0u, 1u) == 0u) {
+            status->w[1] = rank;
+            status->w[2] = blockIdx.x;
+            status->w[3] = peer;
+            status->w[4] = e;
+            status->w[5] = seen;
+            status->w[6] = which;
+            __threadfence_system();
+          }
+          *smem_fail = 1u;
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  return *smem_fail == 0u;
+}
+
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+  __device__ static uint4 add(uint4 a, uint4 b) {
+    uint4 r;
+    r.x = __float_as_uint(__uint_as_float(a.x) + __uint_as_float(b.x));
+    r.y = __float_as_uint(__uint_as_float(a.y) + __uint_as_float(b.y));
+    r.z = __float_as_uint(__uint_as_float(a.z) + __uint_as_float(b.z));
+    r.w = __float_as_uint(__uint_as_float(a.w) + __uint_as_float(b.w));
+    return r;
+  }
+  static constexpr int kPerPack = 4;
+  __device__ static void up(uint4 a, float (&f)[8]) {
+    f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
+    f[4] = f[5] = f[6] = f[7] = 0.f;
+  }
+  __device__ static uint4 down(const float (&f)[8]) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+};
+template <>
+struct Elem<__half> {
+  __device__ static uint32_t add2(uint32_t a, uint32_t b) {
+    __half2 r = __hadd2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  __device__ static uint4 add(uint4 a, uint4 b) { return make_uint4(add2(a.x, b.x), add2(a.y, b.y), add2(a.z, b.z), add2(a.w, b.w)); }
+  static constexpr int kPerPack = 8;
+  __device__ static void up(uint4 a, float (&f)[8]) {
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+  __device__ static uint4 down(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __half2 t = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&t);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  __device__ static uint32_t add2(uint32_t a, uint32_t b) {
+    __nv_bfloat162 r = __hadd2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+  __device__ static uint4 add(uint4 a, uint4 b) { return make_uint4(add2(a.x, b.x), add2(a.y, b.y), add2(a.z, b.z), add2(a.w, b.w)); }
+  static constexpr int kPerPack = 8;
+  __device__ static void up(uint4 a, float (&f)[8]) {
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+  }
+  __device__ static uint4 down(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&t);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+// One 16-byte pack reduced over the NG ranks.  TREE: rank-pair tree in T; else rank order in fp32.
+template <typename T, int NG, bool TREE>
+__device__ __forceinline__ uint4 reduce_pack(const RankData& dp, int64_t idx) {
+  uint4 v[NG];
+#pragma unroll
+  for (int r = 0; r < NG; ++r) v[r] = ld_pack(reinterpret_cast<const uint4*>(dp.ptrs[r]) + idx);
+  if constexpr (TREE) {
+#pragma unroll
+    for (int stride = 1; stride < NG; stride *= 2) {
+#pragma unroll
+      for (int i = 0; i + stride < NG; i += 2 * stride) v[i] = Elem<T>::add(v[i], v[i + stride]);
+    }
+    return v[0];
+  } else {
+    float acc[8], t[8];
+    Elem<T>::up(v[0], acc);
+#pragma unroll
+    for (int r = 1; r < NG; ++r) {
+      Elem<T>::up(v[r], t);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += t[i];
+    }
+    return Elem<T>::down(acc);
+  }
+}
+
+template <typename T, int NG, bool TREE>
+__global__ void __launch_bounds__(kThreads, 1)
+allreduce_oneshot_kernel(const RankData* dp_ptr, RankSignals sg, Signal* self, void* out, int rank, int64_t npacks,
+                         ArStatus* status, uint64_t limit_ns) {
+  __shared__ uint32_t fail;
+  if (threadIdx.x == 0) fail = 0u;
+  const RankData dp = *dp_ptr;
+  if (!block_barrier<NG>(sg, self, rank, status, limit_ns, 1, &fail)) return;
+  uint4* o = reinterpret_cast<uint4*>(out);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < npacks; idx += stride)
+    o[idx] = reduce_pack<T, NG, TREE>(dp, idx);
+  // peers may still be reading this rank's buffer: nobody leaves before everybody is done
+  block_barrier<NG>(sg, self, rank, status, limit_ns, 3, &fail);
+}
+
+template <typename T, int NG, bool TREE>
+__global__ void __launch_bounds__(kThreads, 1)
+allreduce_twoshot_kernel(const RankData* dp_ptr, RankSignals sg, Signal* self, void* out, int rank, int64_t npacks,
+                         ArStatus* status, uint64_t limit_ns) {
+  __shared__ uint32_t fail;
+  if (threadIdx.x == 0) fail = 0u;
+  const RankData dp = *dp_ptr;
+  const int64_t part = npacks / NG;
+  const int64_t start = rank * part;
+  const int64_t end = rank == NG - 1 ? npacks : start + part;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  uint4* scratch[NG];
+#pragma unroll
+  for (int r = 0; r < NG; ++r) scratch[r] = reinterpret_cast<uint4*>(sg.sig[r] + 1);
+
+  if (!block_barrier<NG>(sg, self, rank, status, limit_ns, 1, &fail)) return;
+  // reduce-scatter: this rank owns packs [start, end)
+  for (int64_t idx = start + tid; idx < end; idx += stride) scratch[rank][idx - start] = reduce_pack<T, NG, TREE>(dp, idx);
+  // release this rank's scratch writes / acquire the peers'
+  if (!block_barrier<NG>(sg, self, rank, status, limit_ns, 2, &fail)) return;
+  // all-gather: same thread <-> same pack offset in both phases
+  uint4* o = reinterpret_cast<uint4*>(out);
+  const int64_t largest = part + npacks % NG;
+  for (int64_t idx = tid; idx < largest; idx += stride) {
+#pragma unroll
+    for (int i = 0; i < NG; ++i) {
+      const int src = (rank + i) % NG;
+      if (src == NG - 1 || idx < part) o[src * part + idx] = ld_pack(scratch[src] + idx);
+    }
+  }
+}
+
+// ==================================================================== host object
+struct IpcKey {
+  unsigned char b[sizeof(cudaIpcMemHandle_t)];
+  bool operator<(const IpcKey& o) const { return memcmp(b, o.b, sizeof(b)) < 0; }
+};
+
+struct Communicator {
+  int rank = 0, world = 0;
+  bool full_nvlink = true;
+  RankSignals sg{};
+  Signal* self = nullptr;
+  RankData* rd_next = nullptr;  // next free slot of the caller-owned device table
+  RankData* rd_end = nullptr;
+  std::unordered_map<const void*, RankData*> registered;
+  std::vector<void*> graph_pending;  // inputs seen during stream capture, slots reserved in order
+  std::map<IpcKey, char*> opened;
+  size_t scratch_bytes = 8u << 20;
+  size_t oneshot_max_bytes = 0;  // 0 = built-in policy
+  int max_blocks = 0;            // 0 = built-in policy
+  uint64_t wait_limit_ns = kArWaitLimitNs;
+  ArStatus* status_host = nullptr;
+  ArStatus* status_dev = nullptr;
+  int sm_count = 0;
+  bool poisoned = false;
+};
+
+static Communicator* as_comm(tbik_ar_t h) { return reinterpret_cast<Communicator*>(h); }
+
+template <typename T, int NG, bool TREE>
+static int launch_ar(Communicator* c, const RankData* slot, void* out, int64_t npacks, bool twoshot, int blocks,
+                     cudaStream_t stream) {
+  if (twoshot)
+    allreduce_twoshot_kernel<T, NG, TREE><<<blocks, kThreads, 0, stream>>>(slot, c->sg, c->self, out, c->rank, npacks,
+                                                                            c->status_dev, c->wait_limit_ns);
+  else
+    allreduce_oneshot_kernel<T, NG, TREE><<<blocks, kThreads, 0, stream>>>(slot, c->sg, c->self, out, c->rank, npacks,
+                                                                            c->status_dev, c->wait_limit_ns);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_cuda_error(e, "all-reduce kernel launch");
+  return TBIK_OK;
+}
+
+template <typename T, bool TREE>
+static int dispatch_world(Communicator* c, const RankData* slot, void* out, int64_t npacks, bool twoshot, int blocks,
+                          cudaStream_t stream) {
+  switch (c->world) {
+    case 1:
+      if constexpr (TREE) return launch_ar<T, 1, TREE>(c, slot, out, npacks, false, blocks, stream);
+      break;
+    case 2: return launch_ar<T, 2, TREE>(c, slot, out, npacks, twoshot, blocks, stream);
+    case 4: return launch_ar<T, 4, TREE>(c, slot, out, npacks, twoshot, blocks, stream);
+    case 6:
+      if constexpr (!TREE) return launch_ar<T, 6, TREE>(c, slot, out, npacks, twoshot, blocks, stream);
+      break;
+    case 8: return launch_ar<T, 8, TREE>(c, slot, out, npacks, twoshot, blocks, stream);
+    default: break;
+  }
+  return set_error(TBIK_ERR_SHAPE, TREE ? "tree all-reduce supports 1, 2, 4 or 8 ranks"
+                                        : "all-reduce supports 2, 4, 6 or 8 ranks");
+}
+
+int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, void* reg_buffer, size_t reg_bytes,
+           bool tree, cudaStream_t stream) {
+  Communicator* c = as_comm(h);
+  if (!c) return set_error(TBIK_ERR_ARG, "all-reduce: null communicator");
+  if (c->status_host && c->status_host->w[0] != 0) c->poisoned = true;
+  if (c->poisoned)
+    return set_error(TBIK_ERR_DEVICE, "all-reduce: an earlier call gave up waiting for a peer; the communicator must be rebuilt");
+  const int esz = dtype == TBIK_DTYPE_FP32 ? 4 : 2;
+  if (dtype != TBIK_DTYPE_FP32 && dtype != TBIK_DTYPE_FP16 && dtype != TBIK_DTYPE_BF16)
+    return set_error(TBIK_ERR_DTYPE, "all-reduce supports float32, float16 and bfloat16");
+  if (numel < 0) return set_error(TBIK_ERR_SHAPE, "all-reduce: negative element count");
+  if (numel == 0) return TBIK_OK;
+  if (!inp || !out) return set_error(TBIK_ERR_ARG, "all-reduce: null pointer");
+  const size_t bytes = static_cast<size_t>(numel) * esz;
+  if (bytes % 16 != 0)
+    return set_error(TBIK_ERR_SHAPE, "all-reduce requires the byte size to be a multiple of 16");
+  if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0) return set_error(TBIK_ERR_ALIGN, "all-reduce: out must be 16-byte aligned");
+
+  const void* src = inp;
+  if (reg_buffer) {
+    if (bytes > reg_bytes) return set_error(TBIK_ERR_SHAPE, "all-reduce: input larger than the registered staging buffer");
+    cudaError_t e = cudaMemcpyAsync(reg_buffer, inp, bytes, cudaMemcpyDeviceToDevice, stream);
+    if (e != cudaSuccess) return set_cuda_error(e, "cudaMemcpyAsync(staging)");
+    src = reg_buffer;
+  }
+  if ((reinterpret_cast<uintptr_t>(src) & 15u) != 0) return set_error(TBIK_ERR_ALIGN, "all-reduce: input must be 16-byte aligned");
+
+  // Which slot of the device table describes this buffer on every rank?
+  const RankData* slot = nullptr;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  cudaError_t e = cudaStreamIsCapturing(stream, &cap);
+  if (e != cudaSuccess) return set_cuda_error(e, "cudaStreamIsCapturing");
+  if (cap == cudaStreamCaptureStatusActive) {
+    // Peer addresses are unknown until the handles are exchanged after capture: reserve the slot now.
+    if (c->rd_next + c->graph_pending.size() + 1 > c->rd_end)
+      return set_error(TBIK_ERR_STATE, "all-reduce: rank-data table is full");
+    slot = c->rd_next + c->graph_pending.size();
+    c->graph_pending.push_back(const_cast<void*>(src));
+  } else {
+    auto it = c->registered.find(src);
+    if (it == c->registered.end()) {
+      char msg[128];
+      snprintf(msg, sizeof(msg), "buffer address %llu is not registered!", (unsigned long long)reinterpret_cast<uintptr_t>(src));
+      return set_error(TBIK_ERR_STATE, msg);
+    }
+    slot = it->second;
+  }
+
+  const int64_t npacks = static_cast<int64_t>(bytes / 16);
+  size_t one_max = c->oneshot_max_bytes;
+  if (one_max == 0) one_max = c->world <= 2 ? (1u << 20) : (c->world <= 4 ? (512u << 10) : (256u << 10));
+  bool twoshot = c->world > 1 && bytes > one_max && c->full_nvlink;
+  if (twoshot) {
+    const int64_t part = npacks / c->world + npacks % c->world;
+    if (static_cast<size_t>(part) * 16 > c->scratch_bytes) {
+      if (bytes <= (8u << 20)) twoshot = false;  // fits the one-shot schedule comfortably
+      else return set_error(TBIK_ERR_SHAPE, "all-reduce: message needs more scratch than the meta buffer provides (raise max_size)");
+    }
+  }
+  const int64_t work = twoshot ? (npacks + c->world - 1) / c->world : npacks;
+  int cap_blocks = c->max_blocks > 0 ? c->max_blocks : (bytes <= (512u << 10) ? 36 : c->sm_count);
+  if (cap_blocks > kMaxBlocks) cap_blocks = kMaxBlocks;
+  if (cap_blocks > c->sm_count) cap_blocks = c->sm_count;
+  int blocks = static_cast<int>((work + kThreads - 1) / kThreads);
+  if (blocks > cap_blocks) blocks = cap_blocks;
+  if (blocks < 1) blocks = 1;
+
+  if (dtype == TBIK_DTYPE_FP32)
+    return tree ? dispatch_world<float, true>(c, slot, out, npacks, twoshot, blocks, stream)
+                : dispatch_world<float, false>(c, slot, out, npacks, twoshot, blocks, stream);
+  if (dtype == TBIK_DTYPE_FP16)
+    return tree ? dispatch_world<__half, true>(c, slot, out, npacks, twoshot, blocks, stream)
+                : dispatch_world<__half, false>(c, slot, out, npacks, twoshot, blocks, stream);
+  return tree ? dispatch_world<__nv_bfloat16, true>(c, slot, out, npacks, twoshot, blocks, stream)
+              : dispatch_world<__nv_bfloat16, false>(c, slot, out, npacks, twoshot, blocks, stream);
+}
+
+size_t ar_meta_size() { return sizeof(Signal); }
+
+int ar_create(void* const* signals, int world, int rank, void* rank_data, size_t rank_data_bytes, int full_nvlink,
+              tbik_ar_t* out) {
+  if (!out || !signals) return set_error(TBIK_ERR_ARG, "tbik_ar_create: null pointer");
+  if (world > kMaxRanks) return set_error(TBIK_ERR_SHAPE, "world size > 8 is not supported");
+  if (world < 1 || (world != 1 && world % 2 != 0)) return set_error(TBIK_ERR_SHAPE, "Odd num gpus is not supported for now");
+  if (rank < 0 || rank >= world) return set_error(TBIK_ERR_ARG, "invalid rank passed in");
+  if (!rank_data || rank_data_bytes < sizeof(RankData)) return set_error(TBIK_ERR_ARG, "tbik_ar_create: rank_data table too small");
+  for (int i = 0; i < world; ++i)
+    if (!signals[i]) return set_error(TBIK_ERR_ARG, "tbik_ar_create: null signal pointer");
+  Communicator* c = new Communicator();
+  c->rank = rank;
+  c->world = world;
+  c->full_nvlink = full_nvlink != 0;
+  for (int i = 0; i < world; ++i) c->sg.sig[i] = static_cast<Signal*>(signals[i]);
+  c->self = c->sg.sig[rank];
+  c->rd_next = static_cast<RankData*>(rank_data);
+  c->rd_end = c->rd_next + rank_data_bytes / sizeof(RankData);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&c->sm_count, cudaDevAttrMultiProcessorCount, dev);
+  if (c->sm_count <= 0) c->sm_count = 1;
+  cudaError_t e = cudaHostAlloc(reinterpret_cast<void**>(&c->status_host), sizeof(ArStatus), cudaHostAllocMapped);
+  if (e != cudaSuccess) {
+    delete c;
+    return set_cuda_error(e, "cudaHostAlloc(status)");
+  }
+  memset(c->status_host, 0, sizeof(ArStatus));
+  e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&c->status_dev), c->status_host, 0);
+  if (e != cudaSuccess) {
+    cudaFreeHost(c->status_host);
+    delete c;
+    return set_cuda_error(e, "cudaHostGetDevicePointer(status)");
+  }
+  *out = c;
+  return TBIK_OK;
+}
+
+int ar_destroy(tbik_ar_t h) {
+  Communicator* c = as_comm(h);
+  if (!c) return TBIK_OK;
+  for (auto& kv : c->opened) cudaIpcCloseMemHandle(kv.second);
+  if (c->status_host) cudaFreeHost(c->status_host);
+  delete c;
+  return TBIK_OK;
+}
+
+int ar_configure(tbik_ar_t h, int key, int64_t value) {
+  Communicator* c = as_comm(h);
+  if (!c) return set_error(TBIK_ERR_ARG, "tbik_ar_configure: null communicator");
+  switch (key) {
+    case TBIK_AR_CFG_SCRATCH_BYTES: c->scratch_bytes = static_cast<size_t>(value); return TBIK_OK;
+    case TBIK_AR_CFG_ONESHOT_MAX_BYTES: c->oneshot_max_bytes = static_cast<size_t>(value); return TBIK_OK;
+    case TBIK_AR_CFG_MAX_BLOCKS: c->max_blocks = static_cast<int>(value); return TBIK_OK;
+    case TBIK_AR_CFG_WAIT_LIMIT_NS: c->wait_limit_ns = static_cast<uint64_t>(value); return TBIK_OK;
+    default: return set_error(TBIK_ERR_ARG, "tbik_ar_configure: unknown key");
+  }
+}
+
+int ar_register_buffer(tbik_ar_t h, void* const* ptrs) {
+  Communicator* c = as_comm(h);
+  if (!c || !ptrs) return set_error(TBIK_ERR_ARG, "tbik_ar_register_buffer: null pointer");
+  if (c->rd_next + c->graph_pending.size() + 1 > c->rd_end)
+    return set_error(TBIK_ERR_STATE, "Rank data buffer is overflowed by 1");
+  if (!c->graph_pending.empty())
+    return set_error(TBIK_ERR_STATE, "tbik_ar_register_buffer: graph buffers are pending registration");
+  RankData d{};
+  for (int i = 0; i < c->world; ++i) d.ptrs[i] = ptrs[i];
+  cudaError_t e = cudaMemcpy(c->rd_next, &d, sizeof(d), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return set_cuda_error(e, "cudaMemcpy(rank data)");
+  c->registered[ptrs[c->rank]] = c->rd_next;
+  ++c->rd_next;
+  return TBIK_OK;
+}
+
+int ar_graph_meta_count(tbik_ar_t h, int* n) {
+  Communicator* c = as_comm(h);
+  if (!c || !n) return set_error(TBIK_ERR_ARG, "tbik_ar_graph_meta_count: null pointer");
+  *n = static_cast<int>(c->graph_pending.size());
+  return TBIK_OK;
+}
+
+int ar_graph_meta(tbik_ar_t h, void* handles_out, int64_t* offsets_out) {
+  Communicator* c = as_comm(h);
+  if (!c) return set_error(TBIK_ERR_ARG, "tbik_ar_graph_meta: null communicator");
+  typedef CUresult (*GetAttrFn)(void*, CUpointer_attribute, CUdeviceptr);
+  static GetAttrFn get_attr = nullptr;
+  if (!get_attr && !c->graph_pending.empty()) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuPointerGetAttribute", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return set_error(TBIK_ERR_CUDA, "cuPointerGetAttribute is not available from the driver");
+    get_attr = reinterpret_cast<GetAttrFn>(p);
+  }
+  for (size_t i = 0; i < c->graph_pending.size(); ++i) {
+    void* ptr = c->graph_pending[i];
+    void* base = nullptr;
+    // the handle of an allocation always names its base address
+    if (get_attr(&base, CU_POINTER_ATTRIBUTE_RANGE_START_ADDR, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS)
+      return set_error(TBIK_ERR_CUDA, "failed to get pointer attr");
+    cudaError_t e = cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t*>(static_cast<char*>(handles_out) + i * sizeof(cudaIpcMemHandle_t)), base);
+    if (e != cudaSuccess) return set_cuda_error(e, "cudaIpcGetMemHandle");
+    offsets_out[i] = static_cast<char*>(ptr) - static_cast<char*>(base);
+  }
+  return TBIK_OK;
+}
+
+int ar_register_graph_buffers(tbik_ar_t h, const void* const* handles, const int64_t* const* offsets) {
+  Communicator* c = as_comm(h);
+  if (!c || !handles || !offsets) return set_error(TBIK_ERR_ARG, "tbik_ar_register_graph_buffers: null pointer");
+  const size_t n = c->graph_pending.size();
+  if (c->rd_next + n > c->rd_end) return set_error(TBIK_ERR_STATE, "Rank data buffer is overflowed");
+  if (n == 0) return TBIK_OK;
+  std::vector<RankData> rd(n);
+  for (size_t i = 0; i < n; ++i) {
+    for (int j = 0; j < c->world; ++j) {
+      if (j == c->rank) {
+        rd[i].ptrs[j] = c->graph_pending[i];
+        continue;
+      }
+      IpcKey key;
+      memcpy(key.b, static_cast<const char*>(handles[j]) + i * sizeof(cudaIpcMemHandle_t), sizeof(key.b));
+      auto it = c->opened.find(key);
+      if (it == c->opened.end()) {
+        void* p = nullptr;
+        cudaIpcMemHandle_t hd;
+        memcpy(&hd, key.b, sizeof(hd));
+        cudaError_t e = cudaIpcOpenMemHandle(&p, hd, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return set_cuda_error(e, "cudaIpcOpenMemHandle");
+        it = c->opened.emplace(key, static_cast<char*>(p)).first;
+      }
+      rd[i].ptrs[j] = it->second + offsets[j][i];
+    }
+  }
+  cudaError_t e = cudaMemcpy(c->rd_next, rd.data(), sizeof(RankData) * n, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return set_cuda_error(e, "cudaMemcpy(graph rank data)");
+  c->rd_next += n;
+  c->graph_pending.clear();
+  return TBIK_OK;
+}
+
+int ar_status(tbik_ar_t h, uint32_t out[8]) {
+  Communicator* c = as_comm(h);
+  if (!c || !out) return set_error(TBIK_ERR_ARG, "tbik_ar_status: null pointer");
+  for (int i = 0; i < 8; ++i) out[i] = c->status_host ? c->status_host->w[i] : 0u;
+  return TBIK_OK;
+}
+
+}  // namespace tbik

@@ -1,0 +1,487 @@
+// Tree-ordered row-split GEMM for sm_100a (B200):  C[M,N] = A[M,K] * W[N,K]^T.
+//
+// K is cut into leaves of `leaf` elements.  Each leaf is a run of tcgen05.mma (K=16 per
+// instruction) into a fresh fp32 TMEM accumulator; the finished leaf is rounded ONCE to the
+// input type (bf16 / fp16) and then combined with the other leaves in a fixed tree:
+// level 0 sums F consecutive leaves left to right, the levels above are a perfect binary
+// tree, every node rounded to the input type.  The order of operations for one output
+// element depends only on (K, leaf) -- never on M, on the tile grid or on how many CTAs run --
+// so results are bitwise identical across batch sizes, and a K-shard that starts on a subtree
+// boundary yields exactly the subtree's root.  This is the reduction the reference's Triton
+// kernel performs (src/tbik/tree_based_matmul.py:121-174); here it is laid out for Blackwell:
+//
+//   warp 0      TMA producer: 128x64 A box + 128x64 W box per stage, 128-byte swizzle
+//   warp 1      UMMA issuer : 128x128x16 tcgen05.mma, accumulators double-buffered in TMEM
+//   warp 2      TMEM allocator (512 columns: 2 x 128 accumulator + 256 for the tree stack)
+//   warps 4-11  epilogue: tcgen05.ld the leaf, round, carry-chain combine, final store
+//
+// The tree stack (one partial tile per level) lives in registers (level 0), in the spare TMEM
+// columns (levels 1-4, packed 2 x 16 bit per column) and, for very deep trees, in shared
+// memory (levels 5-6).  The MMA of leaf i+1 overlaps the drain+combine of leaf i.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "ptx_sm100a.cuh"
+#include "tbik_internal.h"
+
+namespace tbik {
+
+constexpr int BM = 128;
+constexpr int BN = 128;
+constexpr int BK = 64;  // one 128-byte swizzle row of 16-bit elements
+constexpr int UMMA_K = 16;
+constexpr uint32_t A_STAGE_BYTES = BM * BK * 2;
+constexpr uint32_t B_STAGE_BYTES = BN * BK * 2;
+constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int NUM_THREADS = 384;
+constexpr int EPI_WARP0 = 4;
+constexpr int NUM_EPI_WARPS = 8;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TMEM_STACK_COL0 = 256;     // first column of the tree stack
+constexpr int TMEM_STACK_LEVELS = 4;          // levels 1..4
+constexpr uint32_t SPILL_LEVEL_BYTES = 32768; // one 128x128 tile of packed 16-bit values
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+
+struct GemmParams {
+  void* C;
+  int64_t ldc;
+  int M, N;
+  int kblocks_per_leaf;  // leaf / 64
+  int T, F, L;           // leaves per tile, level-0 radix, number of levels
+  int tiles_m, tiles_n, group_m;
+  uint32_t* status;      // [0] error code, [1] block, [2] role
+};
+
+struct SmemLayout {
+  uint32_t stages;   // byte offset of stage 0
+  uint32_t spill;
+  uint32_t full, empty, tmem_full, tmem_empty, tmem_ptr, abort_flag;
+  uint32_t total;
+};
+
+template <int STAGES, int SPILL>
+__host__ __device__ constexpr SmemLayout smem_layout() {
+  SmemLayout l{};
+  l.stages = 0;
+  l.spill = STAGES * STAGE_BYTES;
+  l.full = l.spill + SPILL * SPILL_LEVEL_BYTES;
+  l.empty = l.full + 8 * STAGES;
+  l.tmem_full = l.empty + 8 * STAGES;
+  l.tmem_empty = l.tmem_full + 16;
+  l.tmem_ptr = l.tmem_empty + 16;
+  l.abort_flag = l.tmem_ptr + 4;
+  l.total = l.abort_flag + 4 + 1024;  // + slack for the manual 1024-byte alignment
+  return l;
+}
+
+TBIK_DEVICE void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
+  const int group_size = p.group_m * p.tiles_n;
+  const int group_id = tile / group_size;
+  const int first_m = group_id * p.group_m;
+  const int gsz = min(p.tiles_m - first_m, p.group_m);
+  const int local = tile - group_id * group_size;
+  tm = first_m + local % gsz;
+  tn = local / gsz;
+}
+
+template <typename T, int STAGES, int SPILL>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const GemmParams p) {
+  constexpr SmemLayout SL = smem_layout<STAGES, SPILL>();
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + SL.abort_flag);
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_gen + SL.tmem_ptr);
+  auto full_bar = [&](int s) { return smem_base + SL.full + 8u * s; };
+  auto empty_bar = [&](int s) { return smem_base + SL.empty + 8u * s; };
+  auto tfull_bar = [&](int a) { return smem_base + SL.tmem_full + 8u * a; };
+  auto tempty_bar = [&](int a) { return smem_base + SL.tmem_empty + 8u * a; };
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0u;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), NUM_EPI_WARPS);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_base + SL.tmem_ptr, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  int role_failed = 0;  // which role observed the abort (for the status word)
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const int kblocks = p.T * p.kblocks_per_leaf;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        int tm, tn;
+        tile_coords(p, tile, tm, tn);
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+            ok = false;
+            role_failed = 1;
+            break;
+          }
+          mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
+          const uint32_t sa = smem_base + SL.stages + stage * STAGE_BYTES;
+          tma_load_2d(sa, &tmap_a, kb * BK, tm * BM, full_bar(stage));
+          tma_load_2d(sa + A_STAGE_BYTES, &tmap_b, kb * BK, tn * BN, full_bar(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // Give copies that are still in flight time to land before the CTA retires.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ UMMA issuer
+    if (lane == 0) {
+      constexpr uint32_t IDESC = umma_idesc_f16(Pack16<T>::kUmmaFmt, BM, BN);
+      const uint64_t desc_a0 = umma_desc_sw128_kmajor(smem_base + SL.stages);
+      const uint64_t desc_b0 = umma_desc_sw128_kmajor(smem_base + SL.stages + A_STAGE_BYTES);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t leaf_ctr = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        for (int leaf = 0; ok && leaf < p.T; ++leaf, ++leaf_ctr) {
+          const uint32_t a = leaf_ctr & 1u;
+          const uint32_t aphase = (leaf_ctr >> 1) & 1u;
+          if (!mbar_wait_bounded(tempty_bar(a), aphase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
+            ok = false;
+            role_failed = 2;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t tmem_d = tmem_base + a * BN;
+          for (int kb = 0; kb < p.kblocks_per_leaf; ++kb) {
+            if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+              ok = false;
+              role_failed = 3;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint64_t sd = static_cast<uint64_t>(stage) * (STAGE_BYTES >> 4);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t koff = static_cast<uint64_t>(k) * ((UMMA_K * 2) >> 4);
+              umma_f16_ss(tmem_d, desc_a0 + sd + koff, desc_b0 + sd + koff, IDESC, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(empty_bar(stage));
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          if (ok) umma_commit(tfull_bar(a));
+        }
+      }
+    }
+  } else if (warp >= EPI_WARP0) {
+    // ------------------------------------------------------------ epilogue: drain + tree combine
+    const int q = warp & 3;                 // TMEM lane quadrant this warp may access
+    const int h = (warp - EPI_WARP0) >> 2;  // which 64-column half of the accumulator
+    const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
+    const int epi_tid = (warp - EPI_WARP0) * 32 + lane;
+    const bool vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
+    uint32_t* spill = reinterpret_cast<uint32_t*>(smem_gen + SL.spill);
+
+    uint32_t cur[32];
+    uint32_t s0[32];
+    uint32_t leaf_ctr = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      int tm, tn;
+      tile_coords(p, tile, tm, tn);
+      int c0 = 0;       // leaves already summed into the open level-0 group
+      uint32_t g = 0;   // finished level-0 groups of this tile
+      for (int leaf = 0; leaf < p.T; ++leaf, ++leaf_ctr) {
+        const uint32_t a = leaf_ctr & 1u;
+        const uint32_t aphase = (leaf_ctr >> 1) & 1u;
+        if (!mbar_wait_bounded(tfull_bar(a), aphase, abort_flag, WAIT_LIMIT_NS)) {
+          ok = false;
+          role_failed = 4;
+          break;
+        }
+        tc_fence_after_sync();
+        {
+          uint32_t v0[32], v1[32];
+          const uint32_t taddr = tmem_base + lane_off + a * BN + h * 64;
+          tmem_ld32(taddr, v0);
+          tmem_ld32(taddr + 32, v1);
+          tmem_wait_ld();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(a));  // accumulator may be overwritten now
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            cur[j] = Pack16<T>::from_f32(__uint_as_float(v0[2 * j]), __uint_as_float(v0[2 * j + 1]));
+            cur[16 + j] = Pack16<T>::from_f32(__uint_as_float(v1[2 * j]), __uint_as_float(v1[2 * j + 1]));
+          }
+        }
+        // level 0: radix F, sequential
+        if (c0 > 0) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) cur[j] = Pack16<T>::add(s0[j], cur[j]);
+        }
+        if (++c0 < p.F) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) s0[j] = cur[j];
+          continue;
+        }
+        c0 = 0;
+        // levels >= 1: binary counter over finished groups
+        uint32_t gb = g++;
+        int lvl = 1;
+        while (lvl < p.L && (gb & 1u)) {
+          uint32_t t[32];
+          if (lvl <= TMEM_STACK_LEVELS) {
+            tmem_ld32(tmem_base + lane_off + TMEM_STACK_COL0 + (lvl - 1) * 64 + h * 32, t);
+            tmem_wait_ld();
+          } else {
+            const uint32_t* sp = spill + (lvl - 1 - TMEM_STACK_LEVELS) * (SPILL_LEVEL_BYTES / 4);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) t[j] = sp[j * (NUM_EPI_WARPS * 32) + epi_tid];
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) cur[j] = Pack16<T>::add(t[j], cur[j]);
+          gb >>= 1;
+          ++lvl;
+        }
+        if (lvl < p.L) {
+          if (lvl <= TMEM_STACK_LEVELS) {
+            tmem_st32(tmem_base + lane_off + TMEM_STACK_COL0 + (lvl - 1) * 64 + h * 32, cur);
+            tmem_wait_st();
+          } else {
+            uint32_t* sp = spill + (lvl - 1 - TMEM_STACK_LEVELS) * (SPILL_LEVEL_BYTES / 4);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sp[j * (NUM_EPI_WARPS * 32) + epi_tid] = cur[j];
+          }
+        } else {
+          // root of the tile's tree: write C
+          const int row = tm * BM + q * 32 + lane;
+          const int col0 = tn * BN + h * 64;
+          if (row < p.M && col0 < p.N) {
+            T* crow = reinterpret_cast<T*>(p.C) + static_cast<int64_t>(row) * p.ldc + col0;
+            if (vec_ok && col0 + 64 <= p.N) {
+              uint4* dst = reinterpret_cast<uint4*>(crow);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) dst[j] = make_uint4(cur[4 * j], cur[4 * j + 1], cur[4 * j + 2], cur[4 * j + 3]);
+            } else {
+              uint16_t* dst = reinterpret_cast<uint16_t*>(crow);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (col0 + 2 * j < p.N) dst[2 * j] = static_cast<uint16_t>(cur[j] & 0xFFFFu);
+                if (col0 + 2 * j + 1 < p.N) dst[2 * j + 1] = static_cast<uint16_t>(cur[j] >> 16);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- tear-down
+  tc_fence_before_sync();
+  __syncthreads();
+  if (role_failed != 0 && p.status != nullptr) {
+    if (atomicCAS(p.status, 0u, 1u) == 0u) {
+      p.status[1] = blockIdx.x;
+      p.status[2] = static_cast<uint32_t>(role_failed);
+    }
+  }
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ==================================================================== host side
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  }
+  return fn;
+}
+
+// Row-major [rows, K] 16-bit matrix, row stride `ld` elements, box = 64 (K) x 128 rows.
+int make_tmap(CUtensorMap* tm, int dtype, const void* base, int64_t rows, int64_t K, int64_t ld) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return set_error(TBIK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {BK, BM};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = dtype == TBIK_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = fn(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char msg[160];
+    snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld K=%lld ld=%lld)", (int)r,
+             (long long)rows, (long long)K, (long long)ld);
+    return set_error(TBIK_ERR_CUDA, msg);
+  }
+  return TBIK_OK;
+}
+
+__device__ uint32_t g_gemm_status[4];
+
+template <typename T, int STAGES, int SPILL>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
+  constexpr SmemLayout SL = smem_layout<STAGES, SPILL>();
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(tree_gemm_kernel<T, STAGES, SPILL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(SL.total));
+    if (e != cudaSuccess) return set_cuda_error(e, "cudaFuncSetAttribute(tree_gemm_kernel)");
+    configured[dev] = true;
+  }
+  tree_gemm_kernel<T, STAGES, SPILL><<<grid, NUM_THREADS, SL.total, stream>>>(ta, tb, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_cuda_error(e, "tree_gemm_kernel launch");
+  return TBIK_OK;
+}
+
+int sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cached[dev] = n > 0 ? n : 1;
+  }
+  return cached[dev];
+}
+
+}  // namespace
+
+int tree_shape(int64_t K, int leaf, int* T, int* F, int* L) {
+  if (leaf <= 0 || K <= 0 || K % leaf != 0) return TBIK_ERR_SHAPE;
+  int64_t t = K / leaf;
+  int64_t f = t;
+  int l = 1;
+  while (f > 2 && f % 2 == 0) {
+    f /= 2;
+    ++l;
+  }
+  *T = static_cast<int>(t);
+  *F = static_cast<int>(f);
+  *L = l;
+  return TBIK_OK;
+}
+
+int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
+                int dtype, int leaf, int node_dtype, int max_ctas, cudaStream_t stream) {
+  if (dtype != TBIK_DTYPE_BF16 && dtype != TBIK_DTYPE_FP16)
+    return set_error(TBIK_ERR_DTYPE, "tbik_gemm supports bf16 and fp16 operands");
+  if (node_dtype != TBIK_NODE_INPUT)
+    return set_error(TBIK_ERR_DTYPE, "tbik_gemm: only node_dtype = TBIK_NODE_INPUT is implemented");
+  if (M < 0 || N < 0 || K <= 0) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: M, N must be >= 0 and K > 0");
+  if (leaf <= 0 || leaf % BK != 0) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: leaf must be a positive multiple of 64");
+  int T, F, L;
+  if (tree_shape(K, leaf, &T, &F, &L) != TBIK_OK)
+    return set_error(TBIK_ERR_SHAPE, "tbik_gemm: K must be a multiple of the leaf width");
+  if (L > 1 + TMEM_STACK_LEVELS + 2)
+    return set_error(TBIK_ERR_SHAPE, "tbik_gemm: reduction tree deeper than 7 levels is not supported");
+  if (M == 0 || N == 0) return TBIK_OK;
+  if (!A || !W || !C) return set_error(TBIK_ERR_ARG, "tbik_gemm: null pointer");
+  if (lda < K || ldw < K || ldc < N) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: leading dimension smaller than the row");
+  if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(W) & 15u) || (lda % 8) || (ldw % 8))
+    return set_error(TBIK_ERR_ALIGN, "tbik_gemm: A and W must be 16-byte aligned with row strides that are multiples of 8 elements");
+  if (reinterpret_cast<uintptr_t>(C) & 1u) return set_error(TBIK_ERR_ALIGN, "tbik_gemm: C must be 2-byte aligned");
+
+  CUtensorMap ta, tb;
+  int rc = make_tmap(&ta, dtype, A, M, K, lda);
+  if (rc != TBIK_OK) return rc;
+  rc = make_tmap(&tb, dtype, W, N, K, ldw);
+  if (rc != TBIK_OK) return rc;
+
+  GemmParams p{};
+  p.C = C;
+  p.ldc = ldc;
+  p.M = M;
+  p.N = N;
+  p.kblocks_per_leaf = leaf / BK;
+  p.T = T;
+  p.F = F;
+  p.L = L;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.group_m = 8;
+  void* status_ptr = nullptr;
+  cudaGetSymbolAddress(&status_ptr, g_gemm_status);
+  p.status = static_cast<uint32_t*>(status_ptr);
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  int ctas = sm_count();
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  const int grid = num_tiles < ctas ? num_tiles : ctas;
+  const bool spill = L > 1 + TMEM_STACK_LEVELS;
+  if (dtype == TBIK_DTYPE_BF16) {
+    return spill ? launch<__nv_bfloat16, 4, 2>(ta, tb, p, grid, stream) : launch<__nv_bfloat16, 6, 0>(ta, tb, p, grid, stream);
+  }
+  return spill ? launch<__half, 4, 2>(ta, tb, p, grid, stream) : launch<__half, 6, 0>(ta, tb, p, grid, stream);
+}
+
+int gemm_status(uint32_t out[4]) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_gemm_status, sizeof(uint32_t) * 4);
+  if (e != cudaSuccess) return set_cuda_error(e, "cudaMemcpyFromSymbol(g_gemm_status)");
+  if (out[0] != 0) {
+    uint32_t zero[4] = {0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_gemm_status, zero, sizeof(zero));
+  }
+  return TBIK_OK;
+}
+
+}  // namespace tbik

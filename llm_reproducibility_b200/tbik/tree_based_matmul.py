@@ -1,0 +1,80 @@
+"""`matmul_tp_persistent`: tree-ordered, batch- and TP-invariant matmul on B200.
+
+Drop-in for the reference's `src/tbik/tree_based_matmul.py:190-276` (same name, arguments,
+return value and assertions); the Triton kernel behind it is replaced by the hand-written
+tcgen05/TMA kernel in `csrc/tree_gemm_sm100a.cu`, reached through the C ABI (`tbik_gemm`).
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from .. import _lib
+
+# Leaf (K-chunk) width per dtype: the reference's BLOCK_SIZE_K (tree_based_matmul.py:206-231).
+_LEAF = {torch.bfloat16: 256, torch.float16: 256}
+_DTYPE_CODE = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_FP16}
+
+
+def tree_shape(K: int, leaf: int):
+    """(T, F, L) exactly as the reference derives them (tree_based_matmul.py:240-249)."""
+    import ctypes
+    T, F, L = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    _lib.check(_lib.lib().tbik_tree_shape(K, leaf, ctypes.byref(T), ctypes.byref(F), ctypes.byref(L)), "tbik_tree_shape")
+    return T.value, F.value, L.value
+
+
+def _k_major_weight(B: torch.Tensor) -> torch.Tensor:
+    """Return W[N,K] (K contiguous) holding B[K,N]'s values.
+
+    `weight.t()` -- what the row-parallel layer passes -- is already such a view, so this is
+    free on the hot path; any other layout is copied once.
+    """
+    Wt = B.t()
+    if Wt.stride(1) == 1 and Wt.stride(0) % 8 == 0 and Wt.data_ptr() % 16 == 0 and Wt.stride(0) >= Wt.shape[1]:
+        return Wt
+    return Wt.contiguous()
+
+
+def matmul_tp_persistent(A: torch.Tensor, B: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                         *, leaf: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C = A @ B with the K reduction in the fixed tree order; returns a new [M, N] tensor of A's dtype.
+
+    A: [M, K]; B: [K, N] (any strides; a K-contiguous view such as `weight.t()` is used in place).
+    `leaf` (keyword, extension) overrides the leaf width; the default is the reference's 256.
+    """
+    assert A.shape[-1] == B.shape[-2], "Dim doesn't match"
+    assert A.dim() == 2 and B.dim() == 2
+    if not A.is_cuda:
+        raise RuntimeError("matmul_tp_persistent needs CUDA tensors (there is no CPU fallback)")
+    if A.dtype not in _LEAF:
+        raise NotImplementedError(f"matmul_tp_persistent: dtype {A.dtype} is not supported by the sm_100a kernel")
+    assert B.dtype == A.dtype
+    M, K = A.shape
+    _, N = B.shape
+    leaf = leaf or int(os.environ.get("TBIK_LEAF", _LEAF[A.dtype]))
+    assert K % leaf == 0
+    if A.stride(1) != 1 or A.stride(0) % 8 != 0 or A.data_ptr() % 16 != 0 or (M > 1 and A.stride(0) < K):
+        A = A.contiguous()
+    W = _k_major_weight(B)
+    C = out if out is not None else torch.empty((M, N), device=A.device, dtype=A.dtype)
+    assert C.shape == (M, N) and C.stride(1) == 1 and C.dtype == A.dtype
+    with torch.cuda.device(A.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = _lib.lib().tbik_gemm(A.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K,
+                                  max(A.stride(0), K), max(W.stride(0), K), max(C.stride(0), N),
+                                  _DTYPE_CODE[A.dtype], leaf, _lib.NODE_INPUT, stream)
+    _lib.check(rc, "tbik_gemm")
+    if bias is not None:
+        C += bias
+    return C
+
+
+def gemm_device_status():
+    """(code, block, role, _) of the GEMM kernels' bounded-wait watchdog; code 0 = healthy."""
+    import ctypes
+    out = (ctypes.c_uint32 * 4)()
+    _lib.check(_lib.lib().tbik_gemm_status(out), "tbik_gemm_status")
+    return tuple(out)
