@@ -73,6 +73,67 @@ int tbik_gemm_ex(const void* A, const void* W, void* C, int M, int N, int K, int
  * Synchronises with the device.  No counterpart in the reference (its waits are unbounded). */
 int tbik_gemm_status(uint32_t out[4]);
 
+/* ---- cross-GPU all-reduce over IPC-registered buffers --------------------------------------- */
+typedef void* tbik_ar_t;
+
+/* Keys of tbik_ar_configure. */
+#define TBIK_AR_CFG_SCRATCH_BYTES 1     /* bytes available after the signal area of each meta buffer */
+#define TBIK_AR_CFG_ONESHOT_MAX_BYTES 2 /* messages up to this size use the one-shot schedule (0 = built-in) */
+#define TBIK_AR_CFG_MAX_BLOCKS 3        /* upper bound on CTAs per launch (0 = built-in)               */
+#define TBIK_AR_CFG_WAIT_LIMIT_NS 4     /* bound of one cross-GPU barrier wait                          */
+
+/* Size in bytes of the signal (flag) area at the start of every rank's meta buffer.
+ * Replaces: meta_size, mini_allreduce/tbik_kernel/csrc/allreduce/custom_all_reduce.cu:148-150. */
+size_t tbik_ar_meta_size(void);
+
+/* Creates a communicator.  signals[i] = address, in this process, of rank i's meta buffer (signal
+ * area followed by scratch), zero-filled by its owner before the addresses were exchanged.
+ * rank_data = caller-owned device table (64 bytes per registered buffer).  The object owns no
+ * device memory.  world must be 1, 2, 4, 6 or 8.
+ * Replaces: init_custom_ar, custom_all_reduce.cu:14-27 and the CustomAllreduce constructor,
+ *           custom_all_reduce.cuh:360-373. */
+int tbik_ar_create(void* const* signals, int world, int rank, void* rank_data, size_t rank_data_bytes,
+                   int full_nvlink, tbik_ar_t* out);
+
+/* Replaces: dispose, custom_all_reduce.cu:144-146 (closes the IPC handles the object opened). */
+int tbik_ar_destroy(tbik_ar_t comm);
+
+/* Tuning / capacity knobs (see TBIK_AR_CFG_*).  No counterpart in the reference, whose limits are
+ * compile-time constants (custom_all_reduce.cuh:20, 494-506). */
+int tbik_ar_configure(tbik_ar_t comm, int key, int64_t value);
+
+/* Registers one buffer: ptrs[i] = address, in this process, of rank i's copy.
+ * Replaces: register_buffer, custom_all_reduce.cu:152-160 / custom_all_reduce.cuh:411-420. */
+int tbik_ar_register_buffer(tbik_ar_t comm, void* const* ptrs);
+
+/* out = tree-sum over ranks of inp, ((0+1)+(2+3))+((4+5)+(6+7)), adds in the element type.
+ * If reg_buffer != NULL, inp is first copied (on `stream`) into reg_buffer, which must be a
+ * registered buffer of at least numel*elsize bytes; otherwise inp itself must be registered (or
+ * the stream is capturing, in which case inp is queued for tbik_ar_register_graph_buffers).
+ * numel*elsize must be a multiple of 16.  Collective: every rank calls it in the same order.
+ * Replaces: tree_all_reduce, custom_all_reduce.cu:100-142 / tree_allreduce, custom_all_reduce.cuh:523-573. */
+int tbik_ar_tree_allreduce(tbik_ar_t comm, const void* inp, void* out, int64_t numel, int dtype, void* reg_buffer,
+                           size_t reg_buffer_bytes, tbik_stream_t stream);
+
+/* As above with the non-tree arithmetic: fp32 accumulation in rank order, one final rounding.
+ * Replaces: all_reduce, custom_all_reduce.cu:57-98 / allreduce, custom_all_reduce.cuh:462-521. */
+int tbik_ar_allreduce(tbik_ar_t comm, const void* inp, void* out, int64_t numel, int dtype, void* reg_buffer,
+                      size_t reg_buffer_bytes, tbik_stream_t stream);
+
+/* CUDA-graph support: inputs seen while a stream was capturing wait for their peers' addresses.
+ * _count gives their number n; _meta writes n IPC handles (64 bytes each) and n offsets;
+ * _register_graph_buffers takes, per rank, that rank's handles and offsets and fills the slots.
+ * Replaces: get_graph_buffer_ipc_meta / register_graph_buffers, custom_all_reduce.cu:162-181 and
+ *           custom_all_reduce.cuh:384-451. */
+int tbik_ar_graph_meta_count(tbik_ar_t comm, int* n);
+int tbik_ar_graph_meta(tbik_ar_t comm, void* handles_out, int64_t* offsets_out);
+int tbik_ar_register_graph_buffers(tbik_ar_t comm, const void* const* handles, const int64_t* const* offsets);
+
+/* Host-visible status of the communicator's kernels, readable at any time without synchronising:
+ * out[0] 0 = healthy, 1 = a barrier wait ran out; out[1..6] = rank, block, peer, expected epoch,
+ * value seen, barrier id.  No counterpart in the reference (custom_all_reduce.cuh:182,186 spin forever). */
+int tbik_ar_status(tbik_ar_t comm, uint32_t out[8]);
+
 #ifdef __cplusplus
 }
 #endif

@@ -13,7 +13,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libtbik_b200.so")
 
-SOURCES = ["capi.cu", "tree_gemm_sm100a.cu"]
+SOURCES = ["capi.cu", "tree_gemm_sm100a.cu", "tree_allreduce.cu"]
 HEADERS = ["ptx_sm100a.cuh", "tbik_internal.h", os.path.join("..", "..", "include", "tbik.h")]
 
 NVCC_FLAGS = [

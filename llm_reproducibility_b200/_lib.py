@@ -27,7 +27,20 @@ _PROTOTYPES = {
     "tbik_gemm": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
     "tbik_gemm_ex": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _vp]),
     "tbik_gemm_status": (_i32, [ctypes.POINTER(ctypes.c_uint32)]),
+    "tbik_ar_meta_size": (_sz, []),
+    "tbik_ar_create": (_i32, [ctypes.POINTER(_vp), _i32, _i32, _vp, _sz, _i32, ctypes.POINTER(_vp)]),
+    "tbik_ar_destroy": (_i32, [_vp]),
+    "tbik_ar_configure": (_i32, [_vp, _i32, _i64]),
+    "tbik_ar_register_buffer": (_i32, [_vp, ctypes.POINTER(_vp)]),
+    "tbik_ar_tree_allreduce": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp, _sz, _vp]),
+    "tbik_ar_allreduce": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp, _sz, _vp]),
+    "tbik_ar_graph_meta_count": (_i32, [_vp, ctypes.POINTER(_i32)]),
+    "tbik_ar_graph_meta": (_i32, [_vp, _vp, ctypes.POINTER(_i64)]),
+    "tbik_ar_register_graph_buffers": (_i32, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(ctypes.POINTER(_i64))]),
+    "tbik_ar_status": (_i32, [_vp, ctypes.POINTER(ctypes.c_uint32)]),
 }
+
+AR_CFG_SCRATCH_BYTES, AR_CFG_ONESHOT_MAX_BYTES, AR_CFG_MAX_BLOCKS, AR_CFG_WAIT_LIMIT_NS = 1, 2, 3, 4
 
 
 def exported_symbols():

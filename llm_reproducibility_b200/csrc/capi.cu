@@ -50,4 +50,42 @@ int tbik_gemm_status(uint32_t out[4]) {
   return tbik::gemm_status(out);
 }
 
+
+size_t tbik_ar_meta_size(void) { return tbik::ar_meta_size(); }
+
+int tbik_ar_create(void* const* signals, int world, int rank, void* rank_data, size_t rank_data_bytes,
+                   int full_nvlink, tbik_ar_t* out) {
+  return tbik::ar_create(signals, world, rank, rank_data, rank_data_bytes, full_nvlink, out);
+}
+
+int tbik_ar_destroy(tbik_ar_t comm) { return tbik::ar_destroy(comm); }
+
+int tbik_ar_configure(tbik_ar_t comm, int key, int64_t value) { return tbik::ar_configure(comm, key, value); }
+
+int tbik_ar_register_buffer(tbik_ar_t comm, void* const* ptrs) { return tbik::ar_register_buffer(comm, ptrs); }
+
+int tbik_ar_tree_allreduce(tbik_ar_t comm, const void* inp, void* out, int64_t numel, int dtype, void* reg_buffer,
+                           size_t reg_buffer_bytes, tbik_stream_t stream) {
+  return tbik::ar_run(comm, inp, out, numel, dtype, reg_buffer, reg_buffer_bytes, true,
+                      static_cast<cudaStream_t>(stream));
+}
+
+int tbik_ar_allreduce(tbik_ar_t comm, const void* inp, void* out, int64_t numel, int dtype, void* reg_buffer,
+                      size_t reg_buffer_bytes, tbik_stream_t stream) {
+  return tbik::ar_run(comm, inp, out, numel, dtype, reg_buffer, reg_buffer_bytes, false,
+                      static_cast<cudaStream_t>(stream));
+}
+
+int tbik_ar_graph_meta_count(tbik_ar_t comm, int* n) { return tbik::ar_graph_meta_count(comm, n); }
+
+int tbik_ar_graph_meta(tbik_ar_t comm, void* handles_out, int64_t* offsets_out) {
+  return tbik::ar_graph_meta(comm, handles_out, offsets_out);
+}
+
+int tbik_ar_register_graph_buffers(tbik_ar_t comm, const void* const* handles, const int64_t* const* offsets) {
+  return tbik::ar_register_graph_buffers(comm, handles, offsets);
+}
+
+int tbik_ar_status(tbik_ar_t comm, uint32_t out[8]) { return tbik::ar_status(comm, out); }
+
 }  // extern "C"

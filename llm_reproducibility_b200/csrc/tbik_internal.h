@@ -17,4 +17,18 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
                 int dtype, int leaf, int node_dtype, int max_ctas, cudaStream_t stream);
 int gemm_status(uint32_t out[4]);
 
+
+size_t ar_meta_size();
+int ar_create(void* const* signals, int world, int rank, void* rank_data, size_t rank_data_bytes, int full_nvlink,
+              tbik_ar_t* out);
+int ar_destroy(tbik_ar_t h);
+int ar_configure(tbik_ar_t h, int key, int64_t value);
+int ar_register_buffer(tbik_ar_t h, void* const* ptrs);
+int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, void* reg_buffer, size_t reg_bytes,
+           bool tree, cudaStream_t stream);
+int ar_graph_meta_count(tbik_ar_t h, int* n);
+int ar_graph_meta(tbik_ar_t h, void* handles_out, int64_t* offsets_out);
+int ar_register_graph_buffers(tbik_ar_t h, const void* const* handles, const int64_t* const* offsets);
+int ar_status(tbik_ar_t h, uint32_t out[8]);
+
 }  // namespace tbik

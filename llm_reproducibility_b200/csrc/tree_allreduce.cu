@@ -262,8 +262,7 @@ allreduce_twoshot_kernel(const RankData* dp_ptr, RankSignals sg, Signal* self, v
   const int64_t largest = part + npacks % NG;
   for (int64_t idx = tid; idx < largest; idx += stride) {
 #pragma unroll
-    for (int i = 0; i < NG; ++i) {
-      const int src = (rank + i) % NG;
+    for (int src = 0; src < NG; ++src) {
       if (src == NG - 1 || idx < part) o[src * part + idx] = ld_pack(scratch[src] + idx);
     }
   }

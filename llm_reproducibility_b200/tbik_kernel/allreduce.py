@@ -1,0 +1,213 @@
+"""Registration of `torch.ops.tbik_kernel.*` and thin forwarding functions.
+
+Op names and schemas are those of the reference (mini_allreduce/csrc/common_ops_allreduce.cc:37-58,
+mini_allreduce/tbik_kernel/allreduce.py:15-44).  The implementations are calls into the C ABI
+(`include/tbik.h`); there is no Python or CPU arithmetic behind them.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Tuple
+
+import torch
+
+from .. import _lib
+
+_HANDLE_BYTES = 64  # sizeof(cudaIpcMemHandle_t)
+_DTYPE_CODE = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_FP16, torch.float32: _lib.DTYPE_FP32}
+
+try:
+    _lib.lib()
+except Exception as exc:  # the reference raises ImportError when its extension is missing
+    raise ImportError(
+        "libtbik_b200.so failed to load. Build it with:\n  python -m llm_reproducibility_b200._build\n"
+    ) from exc
+
+
+def _ptr_array(values):
+    arr = (ctypes.c_void_p * len(values))()
+    for i, v in enumerate(values):
+        arr[i] = v
+    return arr
+
+
+def _stream_of(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _is_weak_contiguous(t: torch.Tensor) -> bool:
+    return t.is_contiguous() or (
+        t.untyped_storage().nbytes() - t.storage_offset() * t.element_size() == t.numel() * t.element_size())
+
+
+# ------------------------------------------------------------------ implementations
+def _init_custom_ar(ipc_tensors: List[int], rank_data: torch.Tensor, rank: int, full_nvlink: bool) -> int:
+    world = len(ipc_tensors)
+    if world > 8:
+        raise ValueError("world size > 8 is not supported")
+    if world != 1 and world % 2 != 0:
+        raise ValueError("Odd num gpus is not supported for now")
+    if rank < 0 or rank >= world:
+        raise ValueError("invalid rank passed in")
+    out = ctypes.c_void_p()
+    with torch.cuda.device(rank_data.device):
+        rc = _lib.lib().tbik_ar_create(_ptr_array(ipc_tensors), world, rank, rank_data.data_ptr(),
+                                       rank_data.numel() * rank_data.element_size(), int(bool(full_nvlink)),
+                                       ctypes.byref(out))
+    _lib.check(rc, "tbik_ar_create")
+    return int(out.value)
+
+
+def _run(fa: int, inp: torch.Tensor, out: torch.Tensor, reg_buffer: int, reg_buffer_sz_bytes: int, tree: bool) -> None:
+    if inp.dtype != out.dtype:
+        raise RuntimeError("inp and out must have the same dtype")
+    if inp.numel() != out.numel():
+        raise RuntimeError("inp and out must have the same number of elements")
+    if not _is_weak_contiguous(out) or not _is_weak_contiguous(inp):
+        raise RuntimeError("inp and out must be (weakly) contiguous")
+    code = _DTYPE_CODE.get(inp.dtype)
+    if code is None:
+        raise RuntimeError("custom allreduce only supports float32, float16 and bfloat16")
+    fn = _lib.lib().tbik_ar_tree_allreduce if tree else _lib.lib().tbik_ar_allreduce
+    with torch.cuda.device(inp.device):
+        rc = fn(fa, inp.data_ptr(), out.data_ptr(), inp.numel(), code, reg_buffer or None, reg_buffer_sz_bytes,
+                _stream_of(inp))
+    _lib.check(rc, "tbik_ar_tree_allreduce" if tree else "tbik_ar_allreduce")
+
+
+def _all_reduce(fa: int, inp: torch.Tensor, out: torch.Tensor, reg_buffer: int, reg_buffer_sz_bytes: int) -> None:
+    _run(fa, inp, out, reg_buffer, reg_buffer_sz_bytes, tree=False)
+
+
+def _tree_all_reduce(fa: int, inp: torch.Tensor, out: torch.Tensor, reg_buffer: int, reg_buffer_sz_bytes: int) -> None:
+    _run(fa, inp, out, reg_buffer, reg_buffer_sz_bytes, tree=True)
+
+
+def _dispose(fa: int) -> None:
+    _lib.check(_lib.lib().tbik_ar_destroy(fa), "tbik_ar_destroy")
+
+
+def _meta_size() -> int:
+    return int(_lib.lib().tbik_ar_meta_size())
+
+
+def _register_buffer(fa: int, ipc_tensors: List[int]) -> None:
+    _lib.check(_lib.lib().tbik_ar_register_buffer(fa, _ptr_array(ipc_tensors)), "tbik_ar_register_buffer")
+
+
+def _get_graph_buffer_ipc_meta(fa: int) -> Tuple[List[int], List[int]]:
+    n = ctypes.c_int()
+    _lib.check(_lib.lib().tbik_ar_graph_meta_count(fa, ctypes.byref(n)), "tbik_ar_graph_meta_count")
+    handles = (ctypes.c_ubyte * (max(n.value, 1) * _HANDLE_BYTES))()
+    offsets = (ctypes.c_int64 * max(n.value, 1))()
+    _lib.check(_lib.lib().tbik_ar_graph_meta(fa, ctypes.cast(handles, ctypes.c_void_p), offsets), "tbik_ar_graph_meta")
+    return list(handles[: n.value * _HANDLE_BYTES]), list(offsets[: n.value])
+
+
+def _register_graph_buffers(fa: int, handles: List[List[int]], offsets: List[List[int]]) -> None:
+    world = len(handles)
+    keep = []
+    hptrs = (ctypes.c_void_p * world)()
+    optrs = (ctypes.POINTER(ctypes.c_int64) * world)()
+    for r in range(world):
+        hb = (ctypes.c_ubyte * max(len(handles[r]), 1))(*[int(b) & 0xFF for b in handles[r]])
+        ob = (ctypes.c_int64 * max(len(offsets[r]), 1))(*offsets[r])
+        keep += [hb, ob]
+        hptrs[r] = ctypes.cast(hb, ctypes.c_void_p)
+        optrs[r] = ctypes.cast(ob, ctypes.POINTER(ctypes.c_int64))
+    _lib.check(_lib.lib().tbik_ar_register_graph_buffers(fa, hptrs, optrs), "tbik_ar_register_graph_buffers")
+
+
+def _configure(fa: int, key: int, value: int) -> None:
+    _lib.check(_lib.lib().tbik_ar_configure(fa, key, value), "tbik_ar_configure")
+
+
+def _status(fa: int) -> List[int]:
+    out = (ctypes.c_uint32 * 8)()
+    _lib.check(_lib.lib().tbik_ar_status(fa, out), "tbik_ar_status")
+    return list(out)
+
+
+def _tree_matmul(A: torch.Tensor, B: torch.Tensor, bias=None) -> torch.Tensor:
+    from ..tbik.tree_based_matmul import matmul_tp_persistent
+    return matmul_tp_persistent(A, B, bias)
+
+
+# ------------------------------------------------------------------ registration (once per process)
+_REGISTERED = False
+
+
+def _register() -> None:
+    global _REGISTERED, _LIBRARY
+    if _REGISTERED:
+        return
+    lib = torch.library.Library("tbik_kernel", "FRAGMENT")
+    any_key = "CompositeExplicitAutograd"
+    lib.define("get_graph_buffer_ipc_meta(int fa) -> (int[], int[])")
+    lib.impl("get_graph_buffer_ipc_meta", _get_graph_buffer_ipc_meta, any_key)
+    lib.define("register_graph_buffers(int fa, int[][] handles, int[][] offsets) -> ()")
+    lib.impl("register_graph_buffers", _register_graph_buffers, any_key)
+    lib.define("dispose(int fa) -> ()")
+    lib.impl("dispose", _dispose, any_key)
+    lib.define("meta_size() -> int")
+    lib.impl("meta_size", _meta_size, any_key)
+    lib.define("register_buffer(int fa, int[] ipc_tensors) -> ()")
+    lib.impl("register_buffer", _register_buffer, any_key)
+    lib.define("init_custom_ar(int[] ipc_tensors, Tensor rank_data, int rank, bool full_nvlink) -> int")
+    lib.impl("init_custom_ar", _init_custom_ar, "CUDA")
+    lib.define("all_reduce(int fa, Tensor inp, Tensor! out, int reg_buffer, int reg_buffer_sz_bytes) -> ()")
+    lib.impl("all_reduce", _all_reduce, "CUDA")
+    lib.define("tree_all_reduce(int fa, Tensor inp, Tensor! out, int reg_buffer, int reg_buffer_sz_bytes) -> ()")
+    lib.impl("tree_all_reduce", _tree_all_reduce, "CUDA")
+    # additions of this implementation
+    lib.define("configure(int fa, int key, int value) -> ()")
+    lib.impl("configure", _configure, any_key)
+    lib.define("status(int fa) -> int[]")
+    lib.impl("status", _status, any_key)
+    lib.define("tree_matmul(Tensor A, Tensor B, Tensor? bias=None) -> Tensor")
+    lib.impl("tree_matmul", _tree_matmul, "CUDA")
+    _LIBRARY = lib  # keep alive
+    _REGISTERED = True
+
+
+_register()
+
+
+def init_custom_ar(*args, **kwargs):
+    return torch.ops.tbik_kernel.init_custom_ar.default(*args, **kwargs)
+
+
+def dispose(*args, **kwargs):
+    return torch.ops.tbik_kernel.dispose.default(*args, **kwargs)
+
+
+def all_reduce(*args, **kwargs):
+    return torch.ops.tbik_kernel.all_reduce.default(*args, **kwargs)
+
+
+def tree_all_reduce(*args, **kwargs):
+    return torch.ops.tbik_kernel.tree_all_reduce.default(*args, **kwargs)
+
+
+def get_graph_buffer_ipc_meta(*args, **kwargs):
+    return torch.ops.tbik_kernel.get_graph_buffer_ipc_meta.default(*args, **kwargs)
+
+
+def register_buffer(*args, **kwargs):
+    return torch.ops.tbik_kernel.register_buffer.default(*args, **kwargs)
+
+
+def register_graph_buffers(*args, **kwargs):
+    return torch.ops.tbik_kernel.register_graph_buffers.default(*args, **kwargs)
+
+
+def meta_size(*args, **kwargs):
+    return torch.ops.tbik_kernel.meta_size.default(*args, **kwargs)
+
+
+def configure(*args, **kwargs):
+    return torch.ops.tbik_kernel.configure.default(*args, **kwargs)
+
+
+def status(*args, **kwargs):
+    return torch.ops.tbik_kernel.status.default(*args, **kwargs)

@@ -1,0 +1,153 @@
+"""Per-rank bodies of the multi-GPU all-reduce tests (imported by spawned processes)."""
+import torch
+import torch.distributed as dist
+
+
+def _inputs(world, numel, dtype, seed, device):
+    """Every rank regenerates all ranks' inputs (same Philox stream on every GPU)."""
+    xs = []
+    for r in range(world):
+        g = torch.Generator(device=device).manual_seed(seed * 1000 + r)
+        xs.append((torch.randn(numel, generator=g, device=device) * 3.0).to(dtype))
+    return xs
+
+
+def bits(t):
+    return t.contiguous().view(torch.int16 if t.element_size() == 2 else torch.int32)
+
+
+def tree_allreduce_parity(rank, world, cases, max_size):
+    from llm_reproducibility_b200.mini_allreduce import CustomTreeAllreduce
+    from llm_reproducibility_b200.mini_allreduce import custom_all_reduce_ops as ops
+    from llm_reproducibility_b200.tbik.tree_based_all_reduce import tree_all_reduce_sum_native
+    from oracle.tbik_ref import tree_allreduce_ref
+
+    device = torch.device(f"cuda:{rank}")
+    gloo = dist.new_group(backend="gloo")
+    ar = CustomTreeAllreduce(group=gloo, device=device, max_size=max_size)
+    assert not ar.disabled, "communicator disabled on a P2P-capable box"
+    report = []
+    for (numel, dtype, seed) in cases:
+        xs = _inputs(world, numel, dtype, seed, device)
+        want = tree_allreduce_ref(xs)
+        for mode, one_max in (("auto", 0), ("oneshot", 1 << 40), ("twoshot", 1)):
+            if mode == "oneshot" and numel * xs[0].element_size() > (8 << 20):
+                continue
+            ops.configure(ar._ptr, ops.CFG_ONESHOT_MAX_BYTES, one_max)
+            got = ar.custom_tree_all_reduce(xs[rank])
+            assert got is not None, (numel, dtype)
+            torch.cuda.synchronize()
+            ar.check_status()
+            ok = torch.equal(bits(got), bits(want))
+            report.append((numel, str(dtype), mode, ok))
+            assert ok, f"rank {rank}: tree all-reduce differs from oracle: numel={numel} {dtype} {mode}"
+        ops.configure(ar._ptr, ops.CFG_ONESHOT_MAX_BYTES, 0)
+        # the reference's own cross-check: custom kernel vs all_gather + ordered adds
+        native = tree_all_reduce_sum_native(xs[rank], None)
+        assert torch.equal(bits(native), bits(want))
+    # repeated calls reuse flags/epochs correctly
+    xs = _inputs(world, 4096, torch.bfloat16, 77, device)
+    want = tree_allreduce_ref(xs)
+    for _ in range(50):
+        got = ar.custom_tree_all_reduce(xs[rank])
+    torch.cuda.synchronize()
+    assert torch.equal(bits(got), bits(want))
+    # ineligible inputs return None (odd byte size; too large)
+    assert ar.custom_tree_all_reduce(torch.zeros(3, dtype=torch.bfloat16, device=device)) is None
+    assert ar.custom_tree_all_reduce(torch.zeros(max_size, dtype=torch.uint8, device=device).view(torch.bfloat16)) is None
+    dist.barrier()
+    ar.close()
+    return report
+
+
+def linear_allreduce_parity(rank, world):
+    from llm_reproducibility_b200.mini_allreduce import CustomAllreduce
+
+    device = torch.device(f"cuda:{rank}")
+    gloo = dist.new_group(backend="gloo")
+    ar = CustomAllreduce(group=gloo, device=device)
+    assert not ar.disabled
+    for numel, dtype in ((4096, torch.bfloat16), (1 << 20, torch.bfloat16), (8192, torch.float16), (2048, torch.float32)):
+        xs = _inputs(world, numel, dtype, 5, device)
+        acc = xs[0].float()
+        for r in range(1, world):
+            acc = acc + xs[r].float()
+        want = acc.to(dtype)
+        got = ar.custom_all_reduce(xs[rank])
+        torch.cuda.synchronize()
+        assert torch.equal(bits(got), bits(want)), (numel, dtype)
+    dist.barrier()
+    ar.close()
+    return True
+
+
+def graph_capture(rank, world):
+    from llm_reproducibility_b200.mini_allreduce import CustomTreeAllreduce
+    from oracle.tbik_ref import tree_allreduce_ref
+
+    device = torch.device(f"cuda:{rank}")
+    gloo = dist.new_group(backend="gloo")
+    ar = CustomTreeAllreduce(group=gloo, device=device)
+    xs = _inputs(world, 8192, torch.bfloat16, 9, device)
+    want = tree_allreduce_ref(xs)
+    static_in = xs[rank].clone()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with ar.capture():
+        with torch.cuda.stream(stream):
+            warm = ar.custom_tree_all_reduce(static_in)  # not capturing yet: zeros_like
+            assert warm is not None and float(warm.abs().sum()) == 0.0
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                out = ar.custom_tree_all_reduce(static_in)
+    dist.barrier()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    ar.check_status()
+    assert torch.equal(bits(out), bits(want))
+    dist.barrier()
+    ar.close()
+    return True
+
+
+def dispatcher(rank, world):
+    """tree_all_reduce_sum end to end on the NCCL device group, plus the patched layer's forward."""
+    from llm_reproducibility_b200.patch.patch_tp_invariant import row_parallel_forward
+    from llm_reproducibility_b200.tbik import tree_based_all_reduce as tar
+    from llm_reproducibility_b200.tbik.tree_based_matmul import matmul_tp_persistent
+    from oracle.tbik_ref import tree_allreduce_ref
+
+    device = torch.device(f"cuda:{rank}")
+    xs = _inputs(world, 1 << 18, torch.bfloat16, 3, device)
+    y = tar.tree_all_reduce_sum(xs[rank], None)
+    torch.cuda.synchronize()
+    assert tar.custom_ar is not None and not tar.custom_ar.disabled
+    assert torch.equal(bits(y), bits(tree_allreduce_ref(xs)))
+
+    # row-parallel layer: TP result == single-device result, bit for bit
+    M, K, N = 96, 4096, 512
+    g = torch.Generator(device=device).manual_seed(1234)
+    X = torch.randn(M, K, generator=g, device=device).to(torch.bfloat16)
+    W = (torch.randn(N, K, generator=g, device=device) * 0.02).to(torch.bfloat16)
+    ks = K // world
+
+    class Layer:
+        input_is_parallel = False
+        tp_size = world
+        tp_rank = rank
+        weight = W[:, rank * ks:(rank + 1) * ks].contiguous()
+        bias = None
+        skip_bias_add = False
+        reduce_results = True
+        return_bias = False
+        quant_method = object()
+
+    out = row_parallel_forward(Layer(), X)
+    full = matmul_tp_persistent(X, W.t())
+    torch.cuda.synchronize()
+    assert torch.equal(bits(out), bits(full)), "TP result differs from the single-device result"
+    dist.barrier()
+    tar.reset_communicator()
+    return True

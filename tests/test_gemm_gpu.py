@@ -1,0 +1,221 @@
+"""Parity of the sm_100a tree GEMM (called through the C ABI) against the CPU oracle, the golden
+outputs of the reference kernel, and the invariance properties the reference checks.
+
+Bit-exact cases use integer-valued operands: every leaf dot product is then exact in fp32 in any
+summation order, so the only freedom left is the rounding/tree order under test.  With N(0,1) x
+N(0,0.02) operands the order of the 256 fp32 additions inside a leaf (fixed by the tensor core, not
+by this code or the reference's) can move a leaf by one rounding step; those cases are held to a
+mismatch budget and to the oracle's own error against fp64.
+"""
+import ctypes
+import os
+import sys
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "golden"))
+
+from make_golden import MATMUL_CASES, make_inputs  # noqa: E402
+from oracle.tbik_ref import exact_int_inputs, matmul_fp64, normal_inputs, sharded_matmul_ref, tbik_matmul_ref  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+# budget for operands whose leaf sums are not exact in fp32
+MAX_MISMATCH_FRACTION = 2e-3
+MAX_REL_ERR_VS_FP64 = 1.0e-2  # of max|C|; the oracle itself sits at ~6.5e-3 for bf16 nodes
+
+
+def bits(t):
+    return t.contiguous().view(torch.int16)
+
+
+def kmajor(B):
+    """[K,N] view whose memory is K-contiguous, like weight.t() of a row-parallel layer."""
+    return B.cuda().t().contiguous().t()
+
+
+@pytest.fixture(scope="module")
+def mm():
+    from llm_reproducibility_b200.tbik.tree_based_matmul import gemm_device_status, matmul_tp_persistent
+
+    def run(A, B, **kw):
+        C = matmul_tp_persistent(A, B, **kw)
+        torch.cuda.synchronize()
+        assert gemm_device_status()[0] == 0
+        return C
+    return run
+
+
+GOLD = torch.load(os.path.join(HERE, "golden", "matmul_reference_interpreter.pt"))
+FP16_INT_CASES = [c for c in MATMUL_CASES if c[1] == torch.float16 and c[5] == "int"]
+
+
+@pytest.mark.parametrize("case", FP16_INT_CASES, ids=[c[0] for c in FP16_INT_CASES])
+def test_matches_reference_kernel_golden_outputs(mm, case):
+    """CUDA kernel vs the stored outputs of the reference's own Triton kernel (every tree shape)."""
+    name, dt, M, K, N, gen, seed = case
+    A, B = make_inputs(dt, M, K, N, gen, seed)
+    C = mm(A.cuda(), kmajor(B))
+    assert torch.equal(bits(C.cpu()), bits(GOLD[name]))
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,K,N", [
+    (1, 256, 8), (1, 4096, 4096), (16, 12288, 256), (37, 1536, 200), (128, 512, 128), (129, 768, 136),
+    (130, 12800, 128), (256, 4096, 512), (300, 6144, 384), (64, 25600, 128),
+])
+def test_bit_exact_vs_oracle_integer_operands(mm, dt, M, K, N):
+    amax = 15 if dt == torch.bfloat16 else 7
+    A, B = exact_int_inputs(M, K, N, dt, seed=M * 7 + K, amax=amax)
+    C = mm(A.cuda(), kmajor(B))
+    assert torch.equal(bits(C.cpu()), bits(tbik_matmul_ref(A, B)))
+
+
+@pytest.mark.parametrize("K", [16384, 32768])
+def test_deep_trees_use_the_shared_memory_levels(mm, K):
+    """L = 6 and 7: levels above the TMEM stack are kept in shared memory."""
+    A, B = exact_int_inputs(130, K, 136, torch.bfloat16, seed=K, amax=7)
+    C = mm(A.cuda(), kmajor(B))
+    assert torch.equal(bits(C.cpu()), bits(tbik_matmul_ref(A, B)))
+
+
+def test_tree_deeper_than_supported_is_rejected(mm):
+    A = torch.zeros(8, 65536, dtype=torch.bfloat16, device="cuda")
+    B = torch.zeros(65536, 8, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="deeper"):
+        mm(A, kmajor(B.cpu()))
+
+
+@pytest.mark.parametrize("leaf,K", [(128, 3200), (64, 1600), (640, 3200), (512, 4096)])
+def test_other_leaf_widths(mm, leaf, K):
+    """Leaf widths other than 256, e.g. 128 for a K/8 = 3200 shard (Qwen3-32B down_proj at TP=8)."""
+    A, B = exact_int_inputs(40, K, 72, torch.bfloat16, seed=leaf, amax=7)
+    C = mm(A.cuda(), kmajor(B), leaf=leaf)
+    assert torch.equal(bits(C.cpu()), bits(tbik_matmul_ref(A, B, leaf=leaf)))
+
+
+@pytest.mark.parametrize("M,K,N", [(64, 4096, 1024), (256, 12288, 512), (2048, 4096, 4096)])
+def test_normal_operands_within_budget(mm, M, K, N):
+    A, B = normal_inputs(M, K, N, torch.bfloat16, seed=0)
+    C = mm(A.cuda(), kmajor(B)).cpu()
+    ref = tbik_matmul_ref(A, B)
+    mismatch = (bits(C) != bits(ref)).float().mean().item()
+    f64 = matmul_fp64(A, B)
+    scale = f64.abs().max().item()
+    err = (C.double() - f64).abs().max().item() / scale
+    err_ref = (ref.double() - f64).abs().max().item() / scale
+    assert mismatch <= MAX_MISMATCH_FRACTION, mismatch
+    assert err <= MAX_REL_ERR_VS_FP64 and err <= 1.5 * err_ref + 1e-6, (err, err_ref)
+
+
+@pytest.mark.parametrize("K,N", [(4096, 4096), (12288, 4096)])
+@pytest.mark.parametrize("M", [1, 16, 256])
+def test_config2_shard_invariance_vs_oracle(mm, M, K, N):
+    """Qwen3-8B o_proj / down_proj: K shards at tp=1/2/4/8 + rank-pair tree == unsharded, bitwise,
+    and (integer operands) == the oracle's sharded result."""
+    Nn = 512  # a 512-column slice of the layer keeps the CPU oracle fast; tiles are independent in N
+    A, B = exact_int_inputs(M, K, Nn, torch.bfloat16, seed=M + K, amax=7)
+    Ad, Bd = A.cuda(), kmajor(B)
+    full = mm(Ad, Bd)
+    assert torch.equal(bits(full.cpu()), bits(tbik_matmul_ref(A, B)))
+    for tp in (2, 4, 8):
+        ks = K // tp
+        parts = [mm(Ad[:, r * ks:(r + 1) * ks], Bd[r * ks:(r + 1) * ks]) for r in range(tp)]
+        while len(parts) > 1:
+            parts = [parts[i] + parts[i + 1] for i in range(0, len(parts), 2)]
+        assert torch.equal(bits(parts[0]), bits(full)), tp
+        assert torch.equal(bits(parts[0].cpu()), bits(sharded_matmul_ref(A, B, tp))), tp
+
+
+@pytest.mark.parametrize("K,N", [(4096, 4096), (12288, 4096)])
+def test_full_size_invariance_properties(mm, K, N):
+    """M = 8192 (too big for the CPU oracle): batch invariance and shard invariance, bitwise."""
+    g = torch.Generator(device="cuda").manual_seed(K)
+    A = torch.randn(8192, K, generator=g, device="cuda").to(torch.bfloat16)
+    W = (torch.randn(N, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    full = mm(A, W.t())
+    for m in (1, 16, 256, 2048):
+        assert torch.equal(bits(mm(A[:m], W.t())), bits(full[:m])), m
+    off = 4096 + 77  # a row window that starts inside a tile
+    assert torch.equal(bits(mm(A[off:off + 300], W.t())), bits(full[off:off + 300]))
+    for tp in (2, 4, 8):
+        ks = K // tp
+        parts = [mm(A[:, r * ks:(r + 1) * ks], W.t()[r * ks:(r + 1) * ks]) for r in range(tp)]
+        while len(parts) > 1:
+            parts = [parts[i] + parts[i + 1] for i in range(0, len(parts), 2)]
+        assert torch.equal(bits(parts[0]), bits(full)), tp
+    # agreement with an fp32-accumulated product, as a sanity bound on the whole tile grid
+    ref = (A[:512].float() @ W.float().t())
+    rel = ((full[:512].float() - ref).abs().max() / ref.abs().max()).item()
+    assert rel < MAX_REL_ERR_VS_FP64
+
+
+def test_result_does_not_depend_on_cta_count():
+    from llm_reproducibility_b200 import _lib
+    A, B = normal_inputs(700, 1536, 520, torch.bfloat16, seed=5)
+    Ad, W = A.cuda(), B.cuda().t().contiguous()
+    outs = []
+    for ctas in (0, 1, 3, 7, 148):
+        C = torch.empty(700, 520, dtype=torch.bfloat16, device="cuda")
+        rc = _lib.lib().tbik_gemm_ex(Ad.data_ptr(), W.data_ptr(), C.data_ptr(), 700, 520, 1536, 1536, 1536, 520,
+                                     _lib.DTYPE_BF16, 256, _lib.NODE_INPUT, ctas,
+                                     torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        outs.append(C)
+    for C in outs[1:]:
+        assert torch.equal(bits(C), bits(outs[0]))
+
+
+def test_strided_operands_and_output_and_bias(mm):
+    A, B = exact_int_inputs(50, 512, 96, torch.bfloat16, seed=11, amax=7)
+    big = torch.zeros(50, 1024, dtype=torch.bfloat16, device="cuda")
+    big[:, 256:768] = A.cuda()
+    Av = big[:, 256:768]                      # row stride 1024, 16-byte aligned start
+    Bn = B.cuda()                             # N-contiguous [K,N]: copied to K-major once
+    ref = tbik_matmul_ref(A, B)
+    assert torch.equal(bits(mm(Av, Bn).cpu()), bits(ref))
+    odd = big[:, 1:513]                       # misaligned start: wrapper makes it contiguous
+    assert torch.equal(bits(mm(odd, Bn).cpu()), bits(tbik_matmul_ref(odd.cpu(), B)))
+    outbuf = torch.zeros(50, 200, dtype=torch.bfloat16, device="cuda")
+    mm(Av, Bn, out=outbuf[:, 8:104])          # C with a row stride larger than N
+    assert torch.equal(bits(outbuf[:, 8:104].cpu()), bits(ref))
+    assert float(outbuf[:, :8].abs().sum()) == 0 and float(outbuf[:, 104:].abs().sum()) == 0
+    bias = torch.arange(96, dtype=torch.bfloat16, device="cuda")
+    assert torch.equal(bits(mm(Av, Bn, bias).cpu()), bits(ref + bias.cpu()))
+
+
+def test_empty_and_error_paths(mm):
+    from llm_reproducibility_b200 import _lib
+    A = torch.zeros(0, 256, dtype=torch.bfloat16, device="cuda")
+    B = torch.zeros(256, 16, dtype=torch.bfloat16, device="cuda")
+    assert mm(A, kmajor(B.cpu())).shape == (0, 16)
+    with pytest.raises(AssertionError):       # K % 256 != 0, as the reference asserts
+        mm(torch.zeros(4, 320, dtype=torch.bfloat16, device="cuda"), torch.zeros(320, 8, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(NotImplementedError):
+        mm(torch.zeros(4, 256, device="cuda"), torch.zeros(256, 8, device="cuda"))
+    with pytest.raises(RuntimeError, match="CUDA tensors"):
+        from llm_reproducibility_b200.tbik.tree_based_matmul import matmul_tp_persistent
+        matmul_tp_persistent(torch.zeros(4, 256, dtype=torch.bfloat16), torch.zeros(256, 8, dtype=torch.bfloat16))
+    # C ABI level: bad leaf, bad alignment, null pointer
+    L = _lib.lib()
+    x = torch.zeros(256 * 8 + 8, dtype=torch.bfloat16, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    assert L.tbik_gemm(x.data_ptr(), x.data_ptr(), x.data_ptr(), 1, 8, 256, 256, 256, 8, 0, 100, 0, s) == -2
+    assert "leaf" in _lib.last_error()
+    assert L.tbik_gemm(x.data_ptr() + 2, x.data_ptr(), x.data_ptr(), 1, 8, 256, 256, 256, 8, 0, 256, 0, s) == -4
+    assert L.tbik_gemm(None, x.data_ptr(), x.data_ptr(), 1, 8, 256, 256, 256, 8, 0, 256, 0, s) == -1
+    assert L.tbik_gemm(x.data_ptr(), x.data_ptr(), x.data_ptr(), 1, 8, 256, 256, 256, 8, 2, 256, 0, s) == -3
+
+
+def test_simple_matmul_demo_shape(mm):
+    """The reference's self-check (simple_matmul.py): M,K,N = 1024,6144,2048, 4 shards."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    A = torch.randn(1024, 6144, generator=g, device="cuda").to(torch.bfloat16)
+    B = torch.randn(6144, 2048, generator=g, device="cuda").to(torch.bfloat16)
+    full = mm(A, B)
+    assert torch.equal(bits(mm(A[:512], B)), bits(full[:512]))
+    parts = [mm(A[:, i * 1536:(i + 1) * 1536], B[i * 1536:(i + 1) * 1536]) for i in range(4)]
+    assert torch.equal(bits((parts[0] + parts[1]) + (parts[2] + parts[3])), bits(full))
