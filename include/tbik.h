@@ -63,10 +63,11 @@ int tbik_tree_shape(int64_t K, int leaf, int* T, int* F, int* L);
 int tbik_gemm(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
               int dtype, int leaf, int node_dtype, tbik_stream_t stream);
 
-/* As tbik_gemm, but runs on at most `max_ctas` CTAs (0 = one per SM).  The result does not
- * depend on max_ctas; the entry point exists so that tests can prove that. */
+/* As tbik_gemm, with the schedule exposed: at most `max_ctas` CTAs (0 = one per SM) and
+ * `tiling` 0 = automatic, 1 = one CTA per 128x128 tile, 2 = a CTA pair per 256x128 tile.
+ * The result does not depend on either; the entry point exists so that tests can prove that. */
 int tbik_gemm_ex(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
-                 int dtype, int leaf, int node_dtype, int max_ctas, tbik_stream_t stream);
+                 int dtype, int leaf, int node_dtype, int max_ctas, int tiling, tbik_stream_t stream);
 
 /* Reads (and clears) the device-side status of the GEMM kernels on the current device:
  * out[0] != 0 means a kernel gave up on a bounded wait (out[1] = block, out[2] = role).

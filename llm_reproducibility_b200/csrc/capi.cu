@@ -35,13 +35,14 @@ int tbik_tree_shape(int64_t K, int leaf, int* T, int* F, int* L) {
 
 int tbik_gemm(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
               int dtype, int leaf, int node_dtype, tbik_stream_t stream) {
-  return tbik::gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, 0,
+  return tbik::gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, 0, 0,
                            static_cast<cudaStream_t>(stream));
 }
 
 int tbik_gemm_ex(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
-                 int dtype, int leaf, int node_dtype, int max_ctas, tbik_stream_t stream) {
-  return tbik::gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, max_ctas,
+                 int dtype, int leaf, int node_dtype, int max_ctas, int tiling, tbik_stream_t stream) {
+  if (tiling < 0 || tiling > 2) return tbik::set_error(TBIK_ERR_ARG, "tbik_gemm_ex: tiling must be 0, 1 or 2");
+  return tbik::gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, max_ctas, tiling,
                            static_cast<cudaStream_t>(stream));
 }
 

@@ -10,14 +10,23 @@
 // boundary yields exactly the subtree's root.  This is the reduction the reference's Triton
 // kernel performs (src/tbik/tree_based_matmul.py:121-174); here it is laid out for Blackwell:
 //
-//   warp 0      TMA producer: 128x64 A box + 128x64 W box per stage, 128-byte swizzle
-//   warp 1      UMMA issuer : 128x128x16 tcgen05.mma, accumulators double-buffered in TMEM
+//   warp 0      TMA producer: 128x64 A box + W box per stage, 128-byte swizzle
+//   warp 1      UMMA issuer : tcgen05.mma, accumulators double-buffered in TMEM
 //   warp 2      TMEM allocator (512 columns: 2 x 128 accumulator + 256 for the tree stack)
 //   warps 4-11  epilogue: tcgen05.ld the leaf, round, carry-chain combine, final store
 //
 // The tree stack (one partial tile per level) lives in registers (level 0), in the spare TMEM
 // columns (levels 1-4, packed 2 x 16 bit per column) and, for very deep trees, in shared
 // memory (levels 5-6).  The MMA of leaf i+1 overlaps the drain+combine of leaf i.
+//
+// Two tilings share all of this code (template parameter PAIR):
+//   single  one CTA per 128x128 tile, UMMA 128x128x16 (cta_group::1)           -- small M
+//   pair    a cluster of two CTAs per 256x128 tile, UMMA 256x128x16 (cta_group::2): each CTA loads
+//           its own 128 rows of A and HALF of the W tile, which halves the shared-memory and L2
+//           traffic per FLOP; each CTA drains its own 128x128 half of the accumulator.  The
+//           partner CTA tells the leader's UMMA issuer when its half of a stage has landed.
+// Every output element sees the same sequence of K=16 tensor-core steps and the same tree in both
+// tilings, so the two produce identical bits (asserted by the tests on random operands).
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -33,8 +42,8 @@ constexpr int BN = 128;
 constexpr int BK = 64;  // one 128-byte swizzle row of 16-bit elements
 constexpr int UMMA_K = 16;
 constexpr uint32_t A_STAGE_BYTES = BM * BK * 2;
-constexpr uint32_t B_STAGE_BYTES = BN * BK * 2;
-constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+__host__ __device__ constexpr uint32_t b_stage_bytes(bool pair) { return (pair ? BN / 2 : BN) * BK * 2; }
+__host__ __device__ constexpr uint32_t stage_bytes(bool pair) { return A_STAGE_BYTES + b_stage_bytes(pair); }
 constexpr int NUM_THREADS = 384;
 constexpr int EPI_WARP0 = 4;
 constexpr int NUM_EPI_WARPS = 8;
@@ -50,7 +59,7 @@ struct GemmParams {
   int M, N;
   int kblocks_per_leaf;  // leaf / 64
   int T, F, L;           // leaves per tile, level-0 radix, number of levels
-  int tiles_m, tiles_n, group_m;
+  int tiles_m, tiles_n, group_m;  // tiles_m counts 128-row (single) or 256-row (pair) tiles
   uint32_t* status;      // [0] error code, [1] block, [2] role
 };
 
@@ -61,11 +70,11 @@ struct SmemLayout {
   uint32_t total;
 };
 
-template <int STAGES, int SPILL>
+template <int STAGES, int SPILL, bool PAIR>
 __host__ __device__ constexpr SmemLayout smem_layout() {
   SmemLayout l{};
   l.stages = 0;
-  l.spill = STAGES * STAGE_BYTES;
+  l.spill = STAGES * stage_bytes(PAIR);
   l.full = l.spill + SPILL * SPILL_LEVEL_BYTES;
   l.empty = l.full + 8 * STAGES;
   l.tmem_full = l.empty + 8 * STAGES;
@@ -86,11 +95,13 @@ TBIK_DEVICE void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
   tn = local / gsz;
 }
 
-template <typename T, int STAGES, int SPILL>
+template <typename T, int STAGES, int SPILL, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
-  constexpr SmemLayout SL = smem_layout<STAGES, SPILL>();
+  constexpr SmemLayout SL = smem_layout<STAGES, SPILL, PAIR>();
+  constexpr uint32_t STAGE_BYTES = stage_bytes(PAIR);
+  constexpr int TILE_M = PAIR ? 2 * BM : BM;  // rows of C per scheduled tile
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -98,6 +109,11 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n;
+  // scheduling unit: a CTA, or a pair of CTAs (cluster of 2) working on one 256-row tile
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  const int unit = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int num_units = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const bool leader = cta_rank == 0u;
 
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + SL.abort_flag);
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_gen + SL.tmem_ptr);
@@ -106,15 +122,18 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   auto tfull_bar = [&](int a) { return smem_base + SL.tmem_full + 8u * a; };
   auto tempty_bar = [&](int a) { return smem_base + SL.tmem_empty + 8u * a; };
 
+  if constexpr (PAIR) cluster_sync_all();  // both CTAs of the pair are resident before TMEM is shared
+
   if (threadIdx.x == 0) {
     *abort_flag = 0u;
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
+      // pair, leader: its own producer + the partner's "my half has landed" relay
+      mbar_init(full_bar(s), (PAIR && leader) ? 2 : 1);
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
-      mbar_init(tempty_bar(a), NUM_EPI_WARPS);
+      mbar_init(tempty_bar(a), PAIR ? 2 * NUM_EPI_WARPS : NUM_EPI_WARPS);  // pair: both CTAs' warps, on the leader's
     }
     fence_mbar_init();
   }
@@ -123,36 +142,44 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     prefetch_tensormap(&tmap_b);
   }
   if (warp == 2) {
-    tmem_alloc(smem_base + SL.tmem_ptr, TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(smem_base + SL.tmem_ptr, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_base + SL.tmem_ptr, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
   int role_failed = 0;  // which role observed the abort (for the status word)
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ TMA producer (every CTA)
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       const int kblocks = p.T * p.kblocks_per_leaf;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
         int tm, tn;
         tile_coords(p, tile, tm, tn);
+        const int row0 = tm * TILE_M + static_cast<int>(cta_rank) * BM;          // this CTA's rows of A
+        const int wrow0 = tn * BN + (PAIR ? static_cast<int>(cta_rank) * (BN / 2) : 0);  // its rows of W
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
             ok = false;
             role_failed = 1;
             break;
           }
-          mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
           const uint32_t sa = smem_base + SL.stages + stage * STAGE_BYTES;
-          tma_load_2d(sa, &tmap_a, kb * BK, tm * BM, full_bar(stage));
-          tma_load_2d(sa + A_STAGE_BYTES, &tmap_b, kb * BK, tn * BN, full_bar(stage));
+          // every CTA tracks its own bytes on its own barrier
+          mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
+          tma_load_2d(sa, &tmap_a, kb * BK, row0, full_bar(stage));
+          tma_load_2d(sa + A_STAGE_BYTES, &tmap_b, kb * BK, wrow0, full_bar(stage));
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -167,16 +194,47 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ UMMA issuer
-    if (lane == 0) {
-      constexpr uint32_t IDESC = umma_idesc_f16(Pack16<T>::kUmmaFmt, BM, BN);
+    if (PAIR && !leader) {
+      // ---------------------------------------------------------- partner CTA: relay "stage landed" to the leader
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        const int kblocks = p.T * p.kblocks_per_leaf;
+        bool ok = true;
+        for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
+          for (int kb = 0; kb < kblocks; ++kb) {
+            if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
+              ok = false;
+              role_failed = 5;
+              break;
+            }
+            mbar_arrive_cluster(map_to_cta(full_bar(stage), 0));
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+    } else if (lane == 0) {
+    // ------------------------------------------------------------ UMMA issuer (pair: leader CTA only)
+      constexpr uint32_t IDESC = umma_idesc_f16(Pack16<T>::kUmmaFmt, TILE_M, BN);
       const uint64_t desc_a0 = umma_desc_sw128_kmajor(smem_base + SL.stages);
       const uint64_t desc_b0 = umma_desc_sw128_kmajor(smem_base + SL.stages + A_STAGE_BYTES);
       int stage = 0;
       uint32_t phase = 0;
       uint32_t leaf_ctr = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      // completion signal to this CTA's barrier and, for a pair, to the partner's twin barrier
+      auto commit = [&](uint32_t bar) {
+        if constexpr (PAIR) {
+          umma_commit_pair(bar);
+          umma_commit_pair(map_to_cta(bar, 1));
+        } else {
+          umma_commit(bar);
+        }
+      };
+      for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
         for (int leaf = 0; ok && leaf < p.T; ++leaf, ++leaf_ctr) {
           const uint32_t a = leaf_ctr & 1u;
           const uint32_t aphase = (leaf_ctr >> 1) & 1u;
@@ -198,15 +256,18 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
               const uint64_t koff = static_cast<uint64_t>(k) * ((UMMA_K * 2) >> 4);
-              umma_f16_ss(tmem_d, desc_a0 + sd + koff, desc_b0 + sd + koff, IDESC, (kb | k) != 0 ? 1u : 0u);
+              if constexpr (PAIR)
+                umma_f16_ss_pair(tmem_d, desc_a0 + sd + koff, desc_b0 + sd + koff, IDESC, (kb | k) != 0 ? 1u : 0u);
+              else
+                umma_f16_ss(tmem_d, desc_a0 + sd + koff, desc_b0 + sd + koff, IDESC, (kb | k) != 0 ? 1u : 0u);
             }
-            umma_commit(empty_bar(stage));
+            commit(empty_bar(stage));
             if (++stage == STAGES) {
               stage = 0;
               phase ^= 1u;
             }
           }
-          if (ok) umma_commit(tfull_bar(a));
+          if (ok) commit(tfull_bar(a));
         }
       }
     }
@@ -218,12 +279,14 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int epi_tid = (warp - EPI_WARP0) * 32 + lane;
     const bool vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
     uint32_t* spill = reinterpret_cast<uint32_t*>(smem_gen + SL.spill);
+    // "accumulator drained" goes to the UMMA issuer, which lives in the leader CTA
+    const uint32_t tempty0 = PAIR ? map_to_cta(tempty_bar(0), 0) : tempty_bar(0);
 
     uint32_t cur[32];
     uint32_t s0[32];
     uint32_t leaf_ctr = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+    for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
       int tm, tn;
       tile_coords(p, tile, tm, tn);
       int c0 = 0;       // leaves already summed into the open level-0 group
@@ -245,7 +308,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           tmem_wait_ld();
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(tempty_bar(a));  // accumulator may be overwritten now
+          if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * a);  // accumulator may be overwritten now
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             cur[j] = Pack16<T>::from_f32(__uint_as_float(v0[2 * j]), __uint_as_float(v0[2 * j + 1]));
@@ -292,7 +355,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         } else {
           // root of the tile's tree: write C
-          const int row = tm * BM + q * 32 + lane;
+          const int row = tm * TILE_M + static_cast<int>(cta_rank) * BM + q * 32 + lane;
           const int col0 = tn * BN + h * 64;
           if (row < p.M && col0 < p.N) {
             T* crow = reinterpret_cast<T*>(p.C) + static_cast<int64_t>(row) * p.ldc + col0;
@@ -316,7 +379,8 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   // ---------------------------------------------------------------- tear-down
   tc_fence_before_sync();
-  __syncthreads();
+  __syncwarp();
+  if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
   if (role_failed != 0 && p.status != nullptr) {
     if (atomicCAS(p.status, 0u, 1u) == 0u) {
       p.status[1] = blockIdx.x;
@@ -325,7 +389,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
   if (warp == 2) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS); else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -351,13 +415,13 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// Row-major [rows, K] 16-bit matrix, row stride `ld` elements, box = 64 (K) x 128 rows.
-int make_tmap(CUtensorMap* tm, int dtype, const void* base, int64_t rows, int64_t K, int64_t ld) {
+// Row-major [rows, K] 16-bit matrix, row stride `ld` elements, box = 64 (K) x `box_rows` rows.
+int make_tmap(CUtensorMap* tm, int dtype, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return set_error(TBIK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-  cuuint32_t box[2] = {BK, BM};
+  cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMapDataType dt = dtype == TBIK_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = fn(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -373,22 +437,40 @@ int make_tmap(CUtensorMap* tm, int dtype, const void* base, int64_t rows, int64_
 
 __device__ uint32_t g_gemm_status[4];
 
-template <typename T, int STAGES, int SPILL>
+template <typename T, int STAGES, int SPILL, bool PAIR>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
-  constexpr SmemLayout SL = smem_layout<STAGES, SPILL>();
+  constexpr SmemLayout SL = smem_layout<STAGES, SPILL, PAIR>();
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
+  auto kernel = tree_gemm_kernel<T, STAGES, SPILL, PAIR>;
   if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(tree_gemm_kernel<T, STAGES, SPILL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(SL.total));
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SL.total));
     if (e != cudaSuccess) return set_cuda_error(e, "cudaFuncSetAttribute(tree_gemm_kernel)");
     configured[dev] = true;
   }
-  tree_gemm_kernel<T, STAGES, SPILL><<<grid, NUM_THREADS, SL.total, stream>>>(ta, tb, p);
-  cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = SL.total;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, p);
   if (e != cudaSuccess) return set_cuda_error(e, "tree_gemm_kernel launch");
   return TBIK_OK;
+}
+
+template <typename T>
+int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, bool spill, bool pair,
+                   cudaStream_t stream) {
+  if (pair) return spill ? launch<T, 5, 2, true>(ta, tb, p, grid, stream) : launch<T, 8, 0, true>(ta, tb, p, grid, stream);
+  return spill ? launch<T, 4, 2, false>(ta, tb, p, grid, stream) : launch<T, 6, 0, false>(ta, tb, p, grid, stream);
 }
 
 int sm_count() {
@@ -422,7 +504,7 @@ int tree_shape(int64_t K, int leaf, int* T, int* F, int* L) {
 }
 
 int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
-                int dtype, int leaf, int node_dtype, int max_ctas, cudaStream_t stream) {
+                int dtype, int leaf, int node_dtype, int max_ctas, int tiling, cudaStream_t stream) {
   if (dtype != TBIK_DTYPE_BF16 && dtype != TBIK_DTYPE_FP16)
     return set_error(TBIK_ERR_DTYPE, "tbik_gemm supports bf16 and fp16 operands");
   if (node_dtype != TBIK_NODE_INPUT)
@@ -441,10 +523,13 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
     return set_error(TBIK_ERR_ALIGN, "tbik_gemm: A and W must be 16-byte aligned with row strides that are multiples of 8 elements");
   if (reinterpret_cast<uintptr_t>(C) & 1u) return set_error(TBIK_ERR_ALIGN, "tbik_gemm: C must be 2-byte aligned");
 
+  // Tiling: a CTA pair per 256x128 tile once there is more than one 128-row block of C.
+  // tiling: 0 = automatic, 1 = single CTA, 2 = CTA pair (the bits do not depend on it).
+  const bool pair = tiling == 2 || (tiling == 0 && M > BM);
   CUtensorMap ta, tb;
-  int rc = make_tmap(&ta, dtype, A, M, K, lda);
+  int rc = make_tmap(&ta, dtype, A, M, K, lda, BM);
   if (rc != TBIK_OK) return rc;
-  rc = make_tmap(&tb, dtype, W, N, K, ldw);
+  rc = make_tmap(&tb, dtype, W, N, K, ldw, pair ? BN / 2 : BN);
   if (rc != TBIK_OK) return rc;
 
   GemmParams p{};
@@ -456,9 +541,10 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
   p.T = T;
   p.F = F;
   p.L = L;
-  p.tiles_m = (M + BM - 1) / BM;
+  const int tile_m = pair ? 2 * BM : BM;
+  p.tiles_m = (M + tile_m - 1) / tile_m;
   p.tiles_n = (N + BN - 1) / BN;
-  p.group_m = 8;
+  p.group_m = pair ? 4 : 8;
   void* status_ptr = nullptr;
   cudaGetSymbolAddress(&status_ptr, g_gemm_status);
   p.status = static_cast<uint32_t*>(status_ptr);
@@ -466,12 +552,13 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
   const int num_tiles = p.tiles_m * p.tiles_n;
   int ctas = sm_count();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  const int grid = num_tiles < ctas ? num_tiles : ctas;
+  int units = pair ? ctas / 2 : ctas;
+  if (units < 1) units = 1;
+  if (units > num_tiles) units = num_tiles;
+  const int grid = pair ? 2 * units : units;
   const bool spill = L > 1 + TMEM_STACK_LEVELS;
-  if (dtype == TBIK_DTYPE_BF16) {
-    return spill ? launch<__nv_bfloat16, 4, 2>(ta, tb, p, grid, stream) : launch<__nv_bfloat16, 6, 0>(ta, tb, p, grid, stream);
-  }
-  return spill ? launch<__half, 4, 2>(ta, tb, p, grid, stream) : launch<__half, 6, 0>(ta, tb, p, grid, stream);
+  if (dtype == TBIK_DTYPE_BF16) return launch_variant<__nv_bfloat16>(ta, tb, p, grid, spill, pair, stream);
+  return launch_variant<__half>(ta, tb, p, grid, spill, pair, stream);
 }
 
 int gemm_status(uint32_t out[4]) {

@@ -46,6 +46,8 @@ def in_the_same_node_as(pg: ProcessGroup, source_rank: int = 0) -> List[bool]:
 
 
 def _physical_device_id(device: torch.device) -> int:
+    if device.type != "cuda":
+        return 0
     visible = os.environ.get("CUDA_VISIBLE_DEVICES", None)
     ids = list(map(int, visible.split(","))) if visible else list(range(torch.cuda.device_count()))
     return ids[device.index]
@@ -81,7 +83,7 @@ class CustomAllreduce:
         elif isinstance(device, str):
             device = torch.device(device)
         assert isinstance(device, torch.device)
-        if device.index is None:
+        if device.type == "cuda" and device.index is None:
             device = torch.device("cuda", torch.cuda.current_device())
         self.device = device
 

@@ -40,8 +40,8 @@ def kmajor(B):
 def mm():
     from llm_reproducibility_b200.tbik.tree_based_matmul import gemm_device_status, matmul_tp_persistent
 
-    def run(A, B, **kw):
-        C = matmul_tp_persistent(A, B, **kw)
+    def run(A, B, *args, **kw):
+        C = matmul_tp_persistent(A, B, *args, **kw)
         torch.cuda.synchronize()
         assert gemm_device_status()[0] == 0
         return C
@@ -152,21 +152,48 @@ def test_full_size_invariance_properties(mm, K, N):
     assert rel < MAX_REL_ERR_VS_FP64
 
 
-def test_result_does_not_depend_on_cta_count():
+def _gemm_ex(Ad, W, M, N, K, ctas, tiling, dtype_code=0, leaf=256):
     from llm_reproducibility_b200 import _lib
+    C = torch.empty(M, N, dtype=Ad.dtype, device="cuda")
+    rc = _lib.lib().tbik_gemm_ex(Ad.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K, K, K, N,
+                                 dtype_code, leaf, _lib.NODE_INPUT, ctas, tiling,
+                                 torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    return C
+
+
+@pytest.mark.parametrize("tiling", [1, 2])
+def test_result_does_not_depend_on_cta_count(tiling):
     A, B = normal_inputs(700, 1536, 520, torch.bfloat16, seed=5)
     Ad, W = A.cuda(), B.cuda().t().contiguous()
-    outs = []
-    for ctas in (0, 1, 3, 7, 148):
-        C = torch.empty(700, 520, dtype=torch.bfloat16, device="cuda")
-        rc = _lib.lib().tbik_gemm_ex(Ad.data_ptr(), W.data_ptr(), C.data_ptr(), 700, 520, 1536, 1536, 1536, 520,
-                                     _lib.DTYPE_BF16, 256, _lib.NODE_INPUT, ctas,
-                                     torch.cuda.current_stream().cuda_stream)
-        assert rc == 0, _lib.last_error()
-        torch.cuda.synchronize()
-        outs.append(C)
+    outs = [_gemm_ex(Ad, W, 700, 520, 1536, ctas, tiling) for ctas in (0, 1, 2, 3, 7, 148)]
     for C in outs[1:]:
         assert torch.equal(bits(C), bits(outs[0]))
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 512), (100, 4096, 512), (128, 12288, 256), (129, 4096, 384),
+                                   (700, 1536, 520), (2048, 4096, 4096), (4096, 12288, 1024)])
+def test_single_cta_and_cta_pair_tilings_agree_bitwise(M, K, N):
+    """Random (not exactly representable) operands: the 128x128 one-CTA schedule and the 256x128
+    CTA-pair schedule must give the same bits, otherwise results would change with the batch size."""
+    g = torch.Generator(device="cuda").manual_seed(M + K + N)
+    A = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    W = (torch.randn(N, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    one = _gemm_ex(A, W, M, N, K, 0, 1)
+    two = _gemm_ex(A, W, M, N, K, 0, 2)
+    assert torch.equal(bits(one), bits(two))
+    h = torch.randn(M, K, generator=g, device="cuda").to(torch.float16)
+    Wh = W.to(torch.float16)
+    assert torch.equal(bits(_gemm_ex(h, Wh, M, N, K, 0, 1, dtype_code=1)), bits(_gemm_ex(h, Wh, M, N, K, 0, 2, dtype_code=1)))
+
+
+@pytest.mark.parametrize("tiling", [1, 2])
+@pytest.mark.parametrize("M,K,N", [(300, 12288, 384), (130, 12800, 128), (130, 16384, 136), (257, 768, 136)])
+def test_both_tilings_bit_exact_vs_oracle(tiling, M, K, N):
+    A, B = exact_int_inputs(M, K, N, torch.bfloat16, seed=M + K, amax=7)
+    C = _gemm_ex(A.cuda(), B.cuda().t().contiguous(), M, N, K, 0, tiling)
+    assert torch.equal(bits(C.cpu()), bits(tbik_matmul_ref(A, B)))
 
 
 def test_strided_operands_and_output_and_bias(mm):

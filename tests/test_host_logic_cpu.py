@@ -1,0 +1,155 @@
+"""CPU tests: the C ABI's export list, the env switches, and the all-reduce host logic on gloo ranks
+(with tests/fake_backend.py standing in for the CUDA runtime and the native ops)."""
+import ctypes
+import os
+import re
+import sys
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+sys.path.insert(0, HERE)
+
+from _dist_utils import run_ranks  # noqa: E402
+import _host_workers as hw  # noqa: E402
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "tbik.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(tbik_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from llm_reproducibility_b200 import _lib
+    names = _declared_functions()
+    assert len(names) >= 15
+    handle = _lib.lib()
+    for n in names:
+        assert hasattr(handle, n), f"{n} is declared in include/tbik.h but not exported"
+    assert sorted(_lib.exported_symbols()) == names, "ctypes prototypes and include/tbik.h disagree"
+
+
+def test_cabi_calls_that_need_no_gpu():
+    from llm_reproducibility_b200 import _lib
+    L = _lib.lib()
+    assert L.tbik_version() >= 1000
+    T, F, Lv = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    for K, leaf, want in ((4096, 256, (16, 2, 4)), (12288, 256, (48, 3, 5)), (25600, 256, (100, 25, 3)),
+                          (3200, 128, (25, 25, 1)), (256, 256, (1, 1, 1))):
+        assert L.tbik_tree_shape(K, leaf, ctypes.byref(T), ctypes.byref(F), ctypes.byref(Lv)) == 0
+        assert (T.value, F.value, Lv.value) == want
+    assert L.tbik_tree_shape(3200, 256, ctypes.byref(T), ctypes.byref(F), ctypes.byref(Lv)) == -2
+    assert "multiple" in _lib.last_error()
+    assert L.tbik_ar_meta_size() % 128 == 0 and L.tbik_ar_meta_size() > 0
+    out = ctypes.c_void_p()
+    assert L.tbik_ar_create(None, 2, 0, None, 0, 1, ctypes.byref(out)) == -1
+    sig = (ctypes.c_void_p * 9)(*([1] * 9))
+    assert L.tbik_ar_create(sig, 9, 0, 1, 1 << 20, 1, ctypes.byref(out)) == -2 and "world size > 8" in _lib.last_error()
+    assert L.tbik_ar_create(sig, 3, 0, 1, 1 << 20, 1, ctypes.byref(out)) == -2 and "Odd num gpus" in _lib.last_error()
+    assert L.tbik_ar_create(sig, 2, 5, 1, 1 << 20, 1, ctypes.byref(out)) == -1 and "invalid rank" in _lib.last_error()
+
+
+def test_oracle_tree_shape_agrees_with_library():
+    from llm_reproducibility_b200.tbik.tree_based_matmul import tree_shape as lib_shape
+    from oracle.tbik_ref import tree_shape
+    for K in range(256, 256 * 130, 256):
+        assert lib_shape(K, 256) == tree_shape(K, 256)
+
+
+def test_env_switches(monkeypatch):
+    from llm_reproducibility_b200 import utils
+    for k in ("VLLM_BATCH_INVARIANT", "VLLM_TP_INVARIANT", "ALIGN_TRAIN_INFERENCE", "TP_INVARIANT_MATMUL"):
+        monkeypatch.delenv(k, raising=False)
+    assert not utils.batch_invariant_is_enabled() and not utils.tp_invariant_is_enabled()
+    assert not utils.compatible_mode_is_enabled() and not utils.check_invariant_compat()
+    monkeypatch.setenv("VLLM_TP_INVARIANT", "1")
+    with pytest.raises(AssertionError):   # TP invariance needs batch invariance
+        utils.tp_invariant_is_enabled()
+    monkeypatch.setenv("VLLM_BATCH_INVARIANT", "1")
+    assert utils.tp_invariant_is_enabled() and utils.check_invariant_compat()
+    monkeypatch.setenv("VLLM_BATCH_INVARIANT", "yes")   # not an integer -> off
+    assert not utils.batch_invariant_is_enabled()
+    monkeypatch.setenv("TP_INVARIANT_MATMUL", "1")
+    assert utils.tp_invariant_matmul_is_enabled()
+
+
+def test_apply_patches_without_flags_is_a_noop(monkeypatch, capsys):
+    from llm_reproducibility_b200.patch import apply_patches
+    for k in ("VLLM_BATCH_INVARIANT", "VLLM_TP_INVARIANT", "ALIGN_TRAIN_INFERENCE"):
+        monkeypatch.delenv(k, raising=False)
+    apply_patches()
+    assert "No patches applied" in capsys.readouterr().out
+
+
+def test_matmul_wrapper_refuses_cpu_tensors():
+    from llm_reproducibility_b200.tbik.tree_based_matmul import matmul_tp_persistent
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        matmul_tp_persistent(torch.zeros(2, 256, dtype=torch.bfloat16), torch.zeros(256, 8, dtype=torch.bfloat16))
+    with pytest.raises(AssertionError):
+        matmul_tp_persistent(torch.zeros(2, 256), torch.zeros(128, 8))
+
+
+def test_weak_contiguity_rule():
+    from llm_reproducibility_b200.mini_allreduce.custom_all_reduce_utils import is_weak_contiguous
+    A = torch.zeros(3, 3, 3)
+    assert is_weak_contiguous(A) and is_weak_contiguous(A[1:]) and is_weak_contiguous(A.permute(2, 0, 1))
+    assert is_weak_contiguous(A[1:].permute(2, 0, 1))
+    assert not is_weak_contiguous(A[None].expand(2, -1, -1, -1)) and not is_weak_contiguous(A[:, 1:, 1:])
+
+
+def test_full_nvlink_probe_with_fake_nvml():
+    from llm_reproducibility_b200.mini_allreduce.custom_all_reduce_utils import is_full_nvlink
+
+    class FakeNvml:
+        NVML_P2P_CAPS_INDEX_NVLINK, NVML_P2P_STATUS_OK = 2, 0
+
+        class NVMLError(Exception):
+            pass
+
+        def __init__(self, broken=(), raises=False):
+            self.broken, self.raises, self.inits = broken, raises, 0
+
+        def nvmlInit(self):
+            self.inits += 1
+
+        def nvmlShutdown(self):
+            self.inits -= 1
+
+        def nvmlDeviceGetHandleByIndex(self, i):
+            return i
+
+        def nvmlDeviceGetP2PStatus(self, a, b, idx):
+            if self.raises:
+                raise self.NVMLError()
+            return 1 if (a, b) in self.broken else 0
+
+    ok = FakeNvml()
+    assert is_full_nvlink([0, 1, 2, 3], 4, nvml=ok) and ok.inits == 0
+    assert not is_full_nvlink([0, 1, 2, 3], 4, nvml=FakeNvml(broken={(1, 3)}))
+    assert not is_full_nvlink([0, 1], 2, nvml=FakeNvml(raises=True))
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_communicator_lifecycle_on_gloo_ranks(world):
+    assert all(run_ranks(hw.communicator_lifecycle, world, backend="gloo"))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_communicator_disables_itself(world):
+    assert all(run_ranks(hw.disabled_paths, world, backend="gloo"))
+
+
+def test_dispatcher_paths_on_gloo_ranks():
+    assert all(run_ranks(hw.dispatcher_paths, 2, backend="gloo"))
+
+
+def test_native_tree_sum_rejects_non_power_of_two_world():
+    assert all(run_ranks(hw.native_rejects_non_power_of_two, 3, backend="gloo"))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_row_parallel_forward_on_gloo_ranks(world):
+    assert all(run_ranks(hw.row_parallel_layer, world, backend="gloo"))
