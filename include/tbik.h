@@ -57,17 +57,34 @@ int tbik_tree_shape(int64_t K, int leaf, int* T, int* F, int* L);
  *   leaf        leaf width in elements, multiple of 64 (the reference uses 256)
  *   node_dtype  TBIK_NODE_INPUT
  * A and W must be 16-byte aligned with lda, ldw multiples of 8.  M == 0 or N == 0 is a no-op.
- * The kernel is enqueued on `stream`; it needs no workspace and allocates nothing.
+ * The kernel is enqueued on `stream`.  This entry point uses no scratch memory and allocates
+ * nothing: it runs the 128x128 tiling, whose tree stack fits on chip for trees of up to 7 levels
+ * (K <= 64 * 2 * leaf); deeper trees are rejected here and need tbik_gemm_ws.
  * Replaces: matmul_tp_persistent / matmul_kernel_tp_persistent,
  *           src/tbik/tree_based_matmul.py:50-187 and :190-274. */
 int tbik_gemm(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
               int dtype, int leaf, int node_dtype, tbik_stream_t stream);
 
-/* As tbik_gemm, with the schedule exposed: at most `max_ctas` CTAs (0 = one per SM) and
- * `tiling` 0 = automatic, 1 = one CTA per 128x128 tile, 2 = a CTA pair per 256x128 tile.
- * The result does not depend on either; the entry point exists so that tests can prove that. */
+/* Scratch bytes tbik_gemm_ws wants for these sizes on the current device (0 if none).
+ * No counterpart in the reference (its kernel keeps the whole stack in registers). */
+size_t tbik_gemm_workspace_bytes(int M, int N, int64_t K, int leaf);
+
+/* As tbik_gemm, with a caller-owned scratch buffer (16-byte aligned device memory, contents
+ * irrelevant before and after the call, not shared with a concurrently running call).  With
+ * enough scratch the faster 128x256 tiling is used for M > 128: its accumulators fill tensor
+ * memory, so the upper levels of the tree stack are kept in shared memory and, for levels touched
+ * at most once every four leaves, in this buffer.  Same bits as tbik_gemm.
+ * Replaces: the same reference functions as tbik_gemm. */
+int tbik_gemm_ws(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
+                 int dtype, int leaf, int node_dtype, void* workspace, size_t workspace_bytes, tbik_stream_t stream);
+
+/* As tbik_gemm_ws, with the schedule exposed: at most `max_ctas` CTAs (0 = one per SM) and
+ * `tiling` 0 = automatic, 1 = 128x128 tile per CTA, 2 = 256x128 per CTA pair, 3 = 128x256 per CTA,
+ * 4 = 256x256 per CTA pair.  The result does not depend on either; the entry point exists so that
+ * tests can prove that. */
 int tbik_gemm_ex(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
-                 int dtype, int leaf, int node_dtype, int max_ctas, int tiling, tbik_stream_t stream);
+                 int dtype, int leaf, int node_dtype, int max_ctas, int tiling, void* workspace,
+                 size_t workspace_bytes, tbik_stream_t stream);
 
 /* Reads (and clears) the device-side status of the GEMM kernels on the current device:
  * out[0] != 0 means a kernel gave up on a bounded wait (out[1] = block, out[2] = role).

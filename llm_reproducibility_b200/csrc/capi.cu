@@ -35,15 +35,23 @@ int tbik_tree_shape(int64_t K, int leaf, int* T, int* F, int* L) {
 
 int tbik_gemm(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
               int dtype, int leaf, int node_dtype, tbik_stream_t stream) {
-  return tbik::gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, 0, 0,
+  return tbik::gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, 0, 0, nullptr, 0,
+                           static_cast<cudaStream_t>(stream));
+}
+
+size_t tbik_gemm_workspace_bytes(int M, int N, int64_t K, int leaf) { return tbik::gemm_workspace_bytes(M, N, K, leaf); }
+
+int tbik_gemm_ws(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
+                 int dtype, int leaf, int node_dtype, void* workspace, size_t workspace_bytes, tbik_stream_t stream) {
+  return tbik::gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, 0, 0, workspace, workspace_bytes,
                            static_cast<cudaStream_t>(stream));
 }
 
 int tbik_gemm_ex(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
-                 int dtype, int leaf, int node_dtype, int max_ctas, int tiling, tbik_stream_t stream) {
-  if (tiling < 0 || tiling > 2) return tbik::set_error(TBIK_ERR_ARG, "tbik_gemm_ex: tiling must be 0, 1 or 2");
-  return tbik::gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, max_ctas, tiling,
-                           static_cast<cudaStream_t>(stream));
+                 int dtype, int leaf, int node_dtype, int max_ctas, int tiling, void* workspace, size_t workspace_bytes,
+                 tbik_stream_t stream) {
+  return tbik::gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, max_ctas, tiling, workspace,
+                           workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int tbik_gemm_status(uint32_t out[4]) {

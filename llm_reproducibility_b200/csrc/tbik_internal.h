@@ -14,7 +14,9 @@ int set_cuda_error(cudaError_t e, const char* what);
 
 int tree_shape(int64_t K, int leaf, int* T, int* F, int* L);
 int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
-                int dtype, int leaf, int node_dtype, int max_ctas, int tiling, cudaStream_t stream);
+                int dtype, int leaf, int node_dtype, int max_ctas, int tiling, void* workspace, size_t ws_bytes,
+                cudaStream_t stream);
+size_t gemm_workspace_bytes(int M, int N, int64_t K, int leaf);
 int gemm_status(uint32_t out[4]);
 
 

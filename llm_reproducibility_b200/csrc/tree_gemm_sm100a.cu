@@ -11,22 +11,24 @@
 // kernel performs (src/tbik/tree_based_matmul.py:121-174); here it is laid out for Blackwell:
 //
 //   warp 0      TMA producer: 128x64 A box + W box per stage, 128-byte swizzle
-//   warp 1      UMMA issuer : tcgen05.mma, accumulators double-buffered in TMEM
-//   warp 2      TMEM allocator (512 columns: 2 x 128 accumulator + 256 for the tree stack)
-//   warps 4-11  epilogue: tcgen05.ld the leaf, round, carry-chain combine, final store
+//   warp 1      UMMA issuer : tcgen05.mma, two accumulators in TMEM (leaf i+1 runs while leaf i drains)
+//   warp 2      TMEM allocator (all 512 columns)
+//   warps 4-11  epilogue: tcgen05.ld the leaf in 32-column chunks, round, carry-chain combine, store
 //
-// The tree stack (one partial tile per level) lives in registers (level 0), in the spare TMEM
-// columns (levels 1-4, packed 2 x 16 bit per column) and, for very deep trees, in shared
-// memory (levels 5-6).  The MMA of leaf i+1 overlaps the drain+combine of leaf i.
+// The tree stack holds one partial tile per level.  Level 0 stays in registers.  The levels above
+// go, in this order, to spare TMEM columns (packed 2 x 16 bit per column), to shared memory and --
+// only for levels that are touched once every >= 4 leaves -- to a per-CTA slice of a global
+// scratch buffer that stays in L2.  Each epilogue thread only ever touches its own stack words.
 //
-// Two tilings share all of this code (template parameter PAIR):
-//   single  one CTA per 128x128 tile, UMMA 128x128x16 (cta_group::1)           -- small M
-//   pair    a cluster of two CTAs per 256x128 tile, UMMA 256x128x16 (cta_group::2): each CTA loads
-//           its own 128 rows of A and HALF of the W tile, which halves the shared-memory and L2
-//           traffic per FLOP; each CTA drains its own 128x128 half of the accumulator.  The
-//           partner CTA tells the leader's UMMA issuer when its half of a stage has landed.
-// Every output element sees the same sequence of K=16 tensor-core steps and the same tree in both
-// tilings, so the two produce identical bits (asserted by the tests on random operands).
+// Tilings (template parameters BN, PAIR); all give identical bits, asserted by the tests:
+//   BN=128 single   128x128 tile, UMMA 128x128x16; 256 TMEM columns left for 4 stack levels; no scratch.
+//                   Used for small M (more tiles) and when no scratch buffer is supplied.
+//   BN=256 single   128x256 tile, UMMA 128x256x16: the instruction shape that runs the tensor core at
+//                   full rate and needs 25% less shared-memory traffic per FLOP; the accumulators
+//                   fill TMEM, so the stack above level 0 lives in shared memory and scratch.
+//   PAIR            a cluster of two CTAs per tile of 256 rows (cta_group::2): each CTA loads its own
+//                   128 rows of A and half of the W tile and drains its own half of the accumulator;
+//                   the partner CTA tells the leader's UMMA issuer when its half of a stage landed.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -37,20 +39,16 @@
 
 namespace tbik {
 
-constexpr int BM = 128;
-constexpr int BN = 128;
-constexpr int BK = 64;  // one 128-byte swizzle row of 16-bit elements
+constexpr int BM = 128;   // rows of C per CTA
+constexpr int BK = 64;    // one 128-byte swizzle row of 16-bit elements
 constexpr int UMMA_K = 16;
 constexpr uint32_t A_STAGE_BYTES = BM * BK * 2;
-__host__ __device__ constexpr uint32_t b_stage_bytes(bool pair) { return (pair ? BN / 2 : BN) * BK * 2; }
-__host__ __device__ constexpr uint32_t stage_bytes(bool pair) { return A_STAGE_BYTES + b_stage_bytes(pair); }
 constexpr int NUM_THREADS = 384;
 constexpr int EPI_WARP0 = 4;
 constexpr int NUM_EPI_WARPS = 8;
+constexpr int EPI_THREADS = NUM_EPI_WARPS * 32;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TMEM_STACK_COL0 = 256;     // first column of the tree stack
-constexpr int TMEM_STACK_LEVELS = 4;          // levels 1..4
-constexpr uint32_t SPILL_LEVEL_BYTES = 32768; // one 128x128 tile of packed 16-bit values
+constexpr int CHUNK = 32;  // accumulator columns drained per tcgen05.ld
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
 
 struct GemmParams {
@@ -60,30 +58,35 @@ struct GemmParams {
   int kblocks_per_leaf;  // leaf / 64
   int T, F, L;           // leaves per tile, level-0 radix, number of levels
   int tiles_m, tiles_n, group_m;  // tiles_m counts 128-row (single) or 256-row (pair) tiles
+  uint32_t* scratch;     // global stack levels: [cta][level][chunk][word][epilogue thread]
+  int scratch_levels;    // levels per CTA held in `scratch`
   uint32_t* status;      // [0] error code, [1] block, [2] role
 };
 
-struct SmemLayout {
-  uint32_t stages;   // byte offset of stage 0
-  uint32_t spill;
-  uint32_t full, empty, tmem_full, tmem_empty, tmem_ptr, abort_flag;
-  uint32_t total;
+// Static shape of one kernel variant.
+template <int BN, int STAGES, int SLEVELS, bool PAIR>
+struct Cfg {
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;              // rows of W this CTA loads per stage
+  static constexpr uint32_t B_STAGE_BYTES = B_ROWS * BK * 2;
+  static constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int TILE_M = PAIR ? 2 * BM : BM;              // rows of C per scheduled tile
+  static constexpr int COLS_PER_WARP = BN / 2;                   // two warps share a TMEM lane quadrant
+  static constexpr int NCH = COLS_PER_WARP / CHUNK;              // chunks per thread per leaf
+  static constexpr int LEVEL_WORDS = EPI_THREADS * NCH * (CHUNK / 2);  // packed words of one stack level
+  static constexpr int TMEM_LEVELS = (static_cast<int>(TMEM_COLS) - 2 * BN) / (BN / 2);
+  static constexpr uint32_t TMEM_STACK_COL0 = 2 * BN;
+  // shared memory map (offsets from a 1024-byte aligned base)
+  static constexpr uint32_t OFF_STACK = STAGES * STAGE_BYTES;
+  static constexpr uint32_t OFF_FULL = OFF_STACK + SLEVELS * LEVEL_WORDS * 4;
+  static constexpr uint32_t OFF_EMPTY = OFF_FULL + 8 * STAGES;
+  static constexpr uint32_t OFF_TFULL = OFF_EMPTY + 8 * STAGES;
+  static constexpr uint32_t OFF_TEMPTY = OFF_TFULL + 16;
+  static constexpr uint32_t OFF_TMEM_PTR = OFF_TEMPTY + 16;
+  static constexpr uint32_t OFF_ABORT = OFF_TMEM_PTR + 4;
+  static constexpr uint32_t SMEM_BYTES = OFF_ABORT + 4 + 1024;   // + slack for the manual alignment
+  static_assert(BN == 128 || BN == 256, "BN");
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
-
-template <int STAGES, int SPILL, bool PAIR>
-__host__ __device__ constexpr SmemLayout smem_layout() {
-  SmemLayout l{};
-  l.stages = 0;
-  l.spill = STAGES * stage_bytes(PAIR);
-  l.full = l.spill + SPILL * SPILL_LEVEL_BYTES;
-  l.empty = l.full + 8 * STAGES;
-  l.tmem_full = l.empty + 8 * STAGES;
-  l.tmem_empty = l.tmem_full + 16;
-  l.tmem_ptr = l.tmem_empty + 16;
-  l.abort_flag = l.tmem_ptr + 4;
-  l.total = l.abort_flag + 4 + 1024;  // + slack for the manual 1024-byte alignment
-  return l;
-}
 
 TBIK_DEVICE void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
   const int group_size = p.group_m * p.tiles_n;
@@ -95,13 +98,14 @@ TBIK_DEVICE void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
   tn = local / gsz;
 }
 
-template <typename T, int STAGES, int SPILL, bool PAIR>
+template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
-  constexpr SmemLayout SL = smem_layout<STAGES, SPILL, PAIR>();
-  constexpr uint32_t STAGE_BYTES = stage_bytes(PAIR);
-  constexpr int TILE_M = PAIR ? 2 * BM : BM;  // rows of C per scheduled tile
+  using C_ = Cfg<BN, STAGES, SLEVELS, PAIR>;
+  constexpr uint32_t STAGE_BYTES = C_::STAGE_BYTES;
+  constexpr int TILE_M = C_::TILE_M;
+  constexpr int NCH = C_::NCH;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -115,12 +119,12 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int num_units = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
   const bool leader = cta_rank == 0u;
 
-  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + SL.abort_flag);
-  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_gen + SL.tmem_ptr);
-  auto full_bar = [&](int s) { return smem_base + SL.full + 8u * s; };
-  auto empty_bar = [&](int s) { return smem_base + SL.empty + 8u * s; };
-  auto tfull_bar = [&](int a) { return smem_base + SL.tmem_full + 8u * a; };
-  auto tempty_bar = [&](int a) { return smem_base + SL.tmem_empty + 8u * a; };
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + C_::OFF_ABORT);
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem_gen + C_::OFF_TMEM_PTR);
+  auto full_bar = [&](int s) { return smem_base + C_::OFF_FULL + 8u * s; };
+  auto empty_bar = [&](int s) { return smem_base + C_::OFF_EMPTY + 8u * s; };
+  auto tfull_bar = [&](int a) { return smem_base + C_::OFF_TFULL + 8u * a; };
+  auto tempty_bar = [&](int a) { return smem_base + C_::OFF_TEMPTY + 8u * a; };
 
   if constexpr (PAIR) cluster_sync_all();  // both CTAs of the pair are resident before TMEM is shared
 
@@ -143,10 +147,10 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
   if (warp == 2) {
     if constexpr (PAIR) {
-      tmem_alloc_pair(smem_base + SL.tmem_ptr, TMEM_COLS);
+      tmem_alloc_pair(smem_base + C_::OFF_TMEM_PTR, TMEM_COLS);
       tmem_relinquish_pair();
     } else {
-      tmem_alloc(smem_base + SL.tmem_ptr, TMEM_COLS);
+      tmem_alloc(smem_base + C_::OFF_TMEM_PTR, TMEM_COLS);
       tmem_relinquish();
     }
   }
@@ -167,15 +171,15 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
         int tm, tn;
         tile_coords(p, tile, tm, tn);
-        const int row0 = tm * TILE_M + static_cast<int>(cta_rank) * BM;          // this CTA's rows of A
-        const int wrow0 = tn * BN + (PAIR ? static_cast<int>(cta_rank) * (BN / 2) : 0);  // its rows of W
+        const int row0 = tm * TILE_M + static_cast<int>(cta_rank) * BM;                   // this CTA's rows of A
+        const int wrow0 = tn * BN + (PAIR ? static_cast<int>(cta_rank) * C_::B_ROWS : 0);  // its rows of W
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
             ok = false;
             role_failed = 1;
             break;
           }
-          const uint32_t sa = smem_base + SL.stages + stage * STAGE_BYTES;
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
           // every CTA tracks its own bytes on its own barrier
           mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
           tma_load_2d(sa, &tmap_a, kb * BK, row0, full_bar(stage));
@@ -217,10 +221,10 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
     } else if (lane == 0) {
-    // ------------------------------------------------------------ UMMA issuer (pair: leader CTA only)
+      // ---------------------------------------------------------- UMMA issuer (pair: leader CTA only)
       constexpr uint32_t IDESC = umma_idesc_f16(Pack16<T>::kUmmaFmt, TILE_M, BN);
-      const uint64_t desc_a0 = umma_desc_sw128_kmajor(smem_base + SL.stages);
-      const uint64_t desc_b0 = umma_desc_sw128_kmajor(smem_base + SL.stages + A_STAGE_BYTES);
+      const uint64_t desc_a0 = umma_desc_sw128_kmajor(smem_base);
+      const uint64_t desc_b0 = umma_desc_sw128_kmajor(smem_base + A_STAGE_BYTES);
       int stage = 0;
       uint32_t phase = 0;
       uint32_t leaf_ctr = 0;
@@ -274,21 +278,54 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp >= EPI_WARP0) {
     // ------------------------------------------------------------ epilogue: drain + tree combine
     const int q = warp & 3;                 // TMEM lane quadrant this warp may access
-    const int h = (warp - EPI_WARP0) >> 2;  // which 64-column half of the accumulator
+    const int h = (warp - EPI_WARP0) >> 2;  // which half of the accumulator's columns
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
     const int epi_tid = (warp - EPI_WARP0) * 32 + lane;
     const bool vec_ok = (p.ldc % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
-    uint32_t* spill = reinterpret_cast<uint32_t*>(smem_gen + SL.spill);
+    uint32_t* smem_stack = reinterpret_cast<uint32_t*>(smem_gen + C_::OFF_STACK);
+    uint32_t* gl_stack = p.scratch + static_cast<size_t>(blockIdx.x) * p.scratch_levels * C_::LEVEL_WORDS;
     // "accumulator drained" goes to the UMMA issuer, which lives in the leader CTA
     const uint32_t tempty0 = PAIR ? map_to_cta(tempty_bar(0), 0) : tempty_bar(0);
 
-    uint32_t cur[32];
-    uint32_t s0[32];
+    // One 32-column chunk (16 packed words) of stack level `lvl` (>= 1) of this thread.
+    auto stack_load = [&](int lvl, int c, uint32_t (&t)[16]) {
+      const int idx = lvl - 1;
+      if (idx < C_::TMEM_LEVELS) {
+        tmem_ld16(tmem_base + lane_off + C_::TMEM_STACK_COL0 + idx * (BN / 2) + h * (BN / 4) + c * 16, t);
+        tmem_wait_ld();
+      } else if (idx < C_::TMEM_LEVELS + SLEVELS) {
+        const uint32_t* sp = smem_stack + ((idx - C_::TMEM_LEVELS) * NCH + c) * 16 * EPI_THREADS + epi_tid;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) t[j] = sp[j * EPI_THREADS];
+      } else {
+        const uint32_t* gp = gl_stack + ((idx - C_::TMEM_LEVELS - SLEVELS) * NCH + c) * 16 * EPI_THREADS + epi_tid;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) t[j] = gp[j * EPI_THREADS];
+      }
+    };
+    auto stack_store = [&](int lvl, int c, const uint32_t (&v)[16]) {
+      const int idx = lvl - 1;
+      if (idx < C_::TMEM_LEVELS) {
+        tmem_st16(tmem_base + lane_off + C_::TMEM_STACK_COL0 + idx * (BN / 2) + h * (BN / 4) + c * 16, v);
+      } else if (idx < C_::TMEM_LEVELS + SLEVELS) {
+        uint32_t* sp = smem_stack + ((idx - C_::TMEM_LEVELS) * NCH + c) * 16 * EPI_THREADS + epi_tid;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) sp[j * EPI_THREADS] = v[j];
+      } else {
+        uint32_t* gp = gl_stack + ((idx - C_::TMEM_LEVELS - SLEVELS) * NCH + c) * 16 * EPI_THREADS + epi_tid;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) gp[j * EPI_THREADS] = v[j];
+      }
+    };
+
+    uint32_t s0[NCH][16];  // open level-0 group
     uint32_t leaf_ctr = 0;
     bool ok = true;
     for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
       int tm, tn;
       tile_coords(p, tile, tm, tn);
+      const int row = tm * TILE_M + static_cast<int>(cta_rank) * BM + q * 32 + lane;
+      T* crow = reinterpret_cast<T*>(p.C) + static_cast<int64_t>(row) * p.ldc;
       int c0 = 0;       // leaves already summed into the open level-0 group
       uint32_t g = 0;   // finished level-0 groups of this tile
       for (int leaf = 0; leaf < p.T; ++leaf, ++leaf_ctr) {
@@ -300,78 +337,73 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           break;
         }
         tc_fence_after_sync();
-        {
-          uint32_t v0[32], v1[32];
-          const uint32_t taddr = tmem_base + lane_off + a * BN + h * 64;
-          tmem_ld32(taddr, v0);
-          tmem_ld32(taddr + 32, v1);
+        if constexpr (C_::TMEM_LEVELS > 0) tmem_wait_st();  // stack stores of earlier leaves have landed
+        const uint32_t tacc = tmem_base + lane_off + a * BN + h * C_::COLS_PER_WARP;
+        const bool add0 = c0 > 0;
+        const bool close = c0 + 1 == p.F;
+        uint32_t raw[2][32];
+        tmem_ld32(tacc, raw[0]);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
           tmem_wait_ld();
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * a);  // accumulator may be overwritten now
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            cur[j] = Pack16<T>::from_f32(__uint_as_float(v0[2 * j]), __uint_as_float(v0[2 * j + 1]));
-            cur[16 + j] = Pack16<T>::from_f32(__uint_as_float(v1[2 * j]), __uint_as_float(v1[2 * j + 1]));
-          }
-        }
-        // level 0: radix F, sequential
-        if (c0 > 0) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) cur[j] = Pack16<T>::add(s0[j], cur[j]);
-        }
-        if (++c0 < p.F) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) s0[j] = cur[j];
-          continue;
-        }
-        c0 = 0;
-        // levels >= 1: binary counter over finished groups
-        uint32_t gb = g++;
-        int lvl = 1;
-        while (lvl < p.L && (gb & 1u)) {
-          uint32_t t[32];
-          if (lvl <= TMEM_STACK_LEVELS) {
-            tmem_ld32(tmem_base + lane_off + TMEM_STACK_COL0 + (lvl - 1) * 64 + h * 32, t);
-            tmem_wait_ld();
+          if (c + 1 < NCH) {
+            tmem_ld32(tacc + (c + 1) * CHUNK, raw[(c + 1) & 1]);  // next chunk flies while this one is combined
           } else {
-            const uint32_t* sp = spill + (lvl - 1 - TMEM_STACK_LEVELS) * (SPILL_LEVEL_BYTES / 4);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) t[j] = sp[j * (NUM_EPI_WARPS * 32) + epi_tid];
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * a);  // accumulator may be overwritten now
           }
+          uint32_t cur[16];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) cur[j] = Pack16<T>::add(t[j], cur[j]);
-          gb >>= 1;
-          ++lvl;
-        }
-        if (lvl < p.L) {
-          if (lvl <= TMEM_STACK_LEVELS) {
-            tmem_st32(tmem_base + lane_off + TMEM_STACK_COL0 + (lvl - 1) * 64 + h * 32, cur);
-            tmem_wait_st();
+          for (int j = 0; j < 16; ++j)
+            cur[j] = Pack16<T>::from_f32(__uint_as_float(raw[c & 1][2 * j]), __uint_as_float(raw[c & 1][2 * j + 1]));
+          // level 0: radix F, sequential
+          if (add0) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) cur[j] = Pack16<T>::add(s0[c][j], cur[j]);
+          }
+          if (!close) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) s0[c][j] = cur[j];
+            continue;
+          }
+          // levels >= 1: binary counter over finished groups
+          uint32_t gb = g;
+          int lvl = 1;
+          while (lvl < p.L && (gb & 1u)) {
+            uint32_t t[16];
+            stack_load(lvl, c, t);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) cur[j] = Pack16<T>::add(t[j], cur[j]);
+            gb >>= 1;
+            ++lvl;
+          }
+          if (lvl < p.L) {
+            stack_store(lvl, c, cur);
           } else {
-            uint32_t* sp = spill + (lvl - 1 - TMEM_STACK_LEVELS) * (SPILL_LEVEL_BYTES / 4);
+            // root of the tile's tree: write 32 columns of C
+            const int col0 = tn * BN + h * C_::COLS_PER_WARP + c * CHUNK;
+            if (row < p.M && col0 < p.N) {
+              if (vec_ok && col0 + CHUNK <= p.N) {
+                uint4* dst = reinterpret_cast<uint4*>(crow + col0);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) sp[j * (NUM_EPI_WARPS * 32) + epi_tid] = cur[j];
-          }
-        } else {
-          // root of the tile's tree: write C
-          const int row = tm * TILE_M + static_cast<int>(cta_rank) * BM + q * 32 + lane;
-          const int col0 = tn * BN + h * 64;
-          if (row < p.M && col0 < p.N) {
-            T* crow = reinterpret_cast<T*>(p.C) + static_cast<int64_t>(row) * p.ldc + col0;
-            if (vec_ok && col0 + 64 <= p.N) {
-              uint4* dst = reinterpret_cast<uint4*>(crow);
+                for (int j = 0; j < 4; ++j) dst[j] = make_uint4(cur[4 * j], cur[4 * j + 1], cur[4 * j + 2], cur[4 * j + 3]);
+              } else {
+                uint16_t* dst = reinterpret_cast<uint16_t*>(crow + col0);
 #pragma unroll
-              for (int j = 0; j < 8; ++j) dst[j] = make_uint4(cur[4 * j], cur[4 * j + 1], cur[4 * j + 2], cur[4 * j + 3]);
-            } else {
-              uint16_t* dst = reinterpret_cast<uint16_t*>(crow);
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (col0 + 2 * j < p.N) dst[2 * j] = static_cast<uint16_t>(cur[j] & 0xFFFFu);
-                if (col0 + 2 * j + 1 < p.N) dst[2 * j + 1] = static_cast<uint16_t>(cur[j] >> 16);
+                for (int j = 0; j < 16; ++j) {
+                  if (col0 + 2 * j < p.N) dst[2 * j] = static_cast<uint16_t>(cur[j] & 0xFFFFu);
+                  if (col0 + 2 * j + 1 < p.N) dst[2 * j + 1] = static_cast<uint16_t>(cur[j] >> 16);
+                }
               }
             }
           }
+        }
+        if (close) {
+          c0 = 0;
+          ++g;
+        } else {
+          ++c0;
         }
       }
     }
@@ -437,40 +469,74 @@ int make_tmap(CUtensorMap* tm, int dtype, const void* base, int64_t rows, int64_
 
 __device__ uint32_t g_gemm_status[4];
 
-template <typename T, int STAGES, int SPILL, bool PAIR>
+template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
-  constexpr SmemLayout SL = smem_layout<STAGES, SPILL, PAIR>();
+  using C_ = Cfg<BN, STAGES, SLEVELS, PAIR>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kernel = tree_gemm_kernel<T, STAGES, SPILL, PAIR>;
+  auto kernel = tree_gemm_kernel<T, BN, STAGES, SLEVELS, PAIR>;
   if (dev < 64 && !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SL.total));
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(C_::SMEM_BYTES));
     if (e != cudaSuccess) return set_cuda_error(e, "cudaFuncSetAttribute(tree_gemm_kernel)");
     configured[dev] = true;
   }
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
-  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = SL.total;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, p);
-  if (e != cudaSuccess) return set_cuda_error(e, "tree_gemm_kernel launch");
+  if constexpr (PAIR) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = C_::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, p);
+    if (e != cudaSuccess) return set_cuda_error(e, "tree_gemm_kernel launch");
+  } else {
+    kernel<<<grid, NUM_THREADS, C_::SMEM_BYTES, stream>>>(ta, tb, p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return set_cuda_error(e, "tree_gemm_kernel launch");
+  }
   return TBIK_OK;
 }
 
+// The compiled variants.  `levels_on_chip` = stack levels above level 0 that fit TMEM + shared memory.
+struct Variant {
+  int bn;
+  bool pair;
+  int levels_on_chip;
+  int level_bytes;  // bytes of one stack level of one CTA
+};
+
+template <int BN, int STAGES, int SLEVELS, bool PAIR>
+constexpr Variant variant_of() {
+  using C_ = Cfg<BN, STAGES, SLEVELS, PAIR>;
+  return Variant{BN, PAIR, C_::TMEM_LEVELS + SLEVELS, C_::LEVEL_WORDS * 4};
+}
+
+// tiling code -> (shallow, deep) variants; the deep one trades pipeline stages for stack levels
+constexpr Variant kVariants[4][2] = {
+    {variant_of<128, 6, 0, false>(), variant_of<128, 4, 2, false>()},
+    {variant_of<128, 8, 0, true>(), variant_of<128, 5, 2, true>()},
+    {variant_of<256, 3, 1, false>(), variant_of<256, 3, 1, false>()},
+    {variant_of<256, 3, 2, true>(), variant_of<256, 3, 2, true>()},
+};
+
 template <typename T>
-int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, bool spill, bool pair,
+int launch_variant(int tiling, bool deep, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
                    cudaStream_t stream) {
-  if (pair) return spill ? launch<T, 5, 2, true>(ta, tb, p, grid, stream) : launch<T, 8, 0, true>(ta, tb, p, grid, stream);
-  return spill ? launch<T, 4, 2, false>(ta, tb, p, grid, stream) : launch<T, 6, 0, false>(ta, tb, p, grid, stream);
+  switch (tiling) {
+    case 1: return deep ? launch<T, 128, 4, 2, false>(ta, tb, p, grid, stream) : launch<T, 128, 6, 0, false>(ta, tb, p, grid, stream);
+    case 2: return deep ? launch<T, 128, 5, 2, true>(ta, tb, p, grid, stream) : launch<T, 128, 8, 0, true>(ta, tb, p, grid, stream);
+    case 3: return launch<T, 256, 3, 1, false>(ta, tb, p, grid, stream);
+    case 4: return launch<T, 256, 3, 2, true>(ta, tb, p, grid, stream);
+    default: return set_error(TBIK_ERR_ARG, "unknown tiling");
+  }
 }
 
 int sm_count() {
@@ -503,33 +569,94 @@ int tree_shape(int64_t K, int leaf, int* T, int* F, int* L) {
   return TBIK_OK;
 }
 
+// Schedule for one call: which variant, how many CTAs, how much scratch.
+struct Plan {
+  int tiling;  // 1..4
+  bool deep;
+  int grid;
+  int tiles_m, tiles_n;
+  int scratch_levels;
+  size_t scratch_bytes;
+};
+
+static Plan make_plan(int tiling, int M, int N, int L, int max_ctas) {
+  Plan pl{};
+  pl.tiling = tiling;
+  const Variant& shallow = kVariants[tiling - 1][0];
+  pl.deep = (L - 1) > shallow.levels_on_chip;
+  const Variant& v = kVariants[tiling - 1][pl.deep ? 1 : 0];
+  const int tile_m = v.pair ? 2 * BM : BM;
+  pl.tiles_m = (M + tile_m - 1) / tile_m;
+  pl.tiles_n = (N + v.bn - 1) / v.bn;
+  const int num_tiles = pl.tiles_m * pl.tiles_n;
+  int ctas = sm_count();
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  int units = v.pair ? ctas / 2 : ctas;
+  if (units < 1) units = 1;
+  if (units > num_tiles) units = num_tiles;
+  pl.grid = v.pair ? 2 * units : units;
+  pl.scratch_levels = (L - 1) > v.levels_on_chip ? (L - 1) - v.levels_on_chip : 0;
+  pl.scratch_bytes = static_cast<size_t>(pl.grid) * pl.scratch_levels * v.level_bytes;
+  return pl;
+}
+
+// Automatic choice: one 128x128 tile per CTA while M fits a single row block (more tiles, no scratch);
+// 128x256 tiles beyond that, if the caller's scratch buffer is large enough for the tree's upper levels.
+static Plan auto_plan(int M, int N, int L, int max_ctas, size_t ws_bytes, bool have_ws) {
+  if (M > BM) {
+    Plan wide = make_plan(3, M, N, L, max_ctas);
+    if (wide.scratch_bytes == 0 || (have_ws && wide.scratch_bytes <= ws_bytes)) return wide;
+  }
+  return make_plan(1, M, N, L, max_ctas);
+}
+
+size_t gemm_workspace_bytes(int M, int N, int64_t K, int leaf) {
+  int T, F, L;
+  if (M <= 0 || N <= 0 || tree_shape(K, leaf, &T, &F, &L) != TBIK_OK) return 0;
+  size_t need = 0;
+  if (M > BM) need = make_plan(3, M, N, L, 0).scratch_bytes;
+  const size_t narrow = make_plan(1, M, N, L, 0).scratch_bytes;
+  return need > narrow ? need : narrow;
+}
+
 int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
-                int dtype, int leaf, int node_dtype, int max_ctas, int tiling, cudaStream_t stream) {
+                int dtype, int leaf, int node_dtype, int max_ctas, int tiling, void* workspace, size_t ws_bytes,
+                cudaStream_t stream) {
   if (dtype != TBIK_DTYPE_BF16 && dtype != TBIK_DTYPE_FP16)
     return set_error(TBIK_ERR_DTYPE, "tbik_gemm supports bf16 and fp16 operands");
   if (node_dtype != TBIK_NODE_INPUT)
     return set_error(TBIK_ERR_DTYPE, "tbik_gemm: only node_dtype = TBIK_NODE_INPUT is implemented");
   if (M < 0 || N < 0 || K <= 0) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: M, N must be >= 0 and K > 0");
   if (leaf <= 0 || leaf % BK != 0) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: leaf must be a positive multiple of 64");
+  if (tiling < 0 || tiling > 4) return set_error(TBIK_ERR_ARG, "tbik_gemm: tiling must be 0..4");
   int T, F, L;
   if (tree_shape(K, leaf, &T, &F, &L) != TBIK_OK)
     return set_error(TBIK_ERR_SHAPE, "tbik_gemm: K must be a multiple of the leaf width");
-  if (L > 1 + TMEM_STACK_LEVELS + 2)
-    return set_error(TBIK_ERR_SHAPE, "tbik_gemm: reduction tree deeper than 7 levels is not supported");
+  if (L > 16) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: reduction tree deeper than 16 levels is not supported");
   if (M == 0 || N == 0) return TBIK_OK;
   if (!A || !W || !C) return set_error(TBIK_ERR_ARG, "tbik_gemm: null pointer");
   if (lda < K || ldw < K || ldc < N) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: leading dimension smaller than the row");
   if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(W) & 15u) || (lda % 8) || (ldw % 8))
     return set_error(TBIK_ERR_ALIGN, "tbik_gemm: A and W must be 16-byte aligned with row strides that are multiples of 8 elements");
   if (reinterpret_cast<uintptr_t>(C) & 1u) return set_error(TBIK_ERR_ALIGN, "tbik_gemm: C must be 2-byte aligned");
+  if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 15u))
+    return set_error(TBIK_ERR_ALIGN, "tbik_gemm: workspace must be 16-byte aligned");
+  const bool have_ws = workspace != nullptr && ws_bytes > 0;
 
-  // Tiling: a CTA pair per 256x128 tile once there is more than one 128-row block of C.
-  // tiling: 0 = automatic, 1 = single CTA, 2 = CTA pair (the bits do not depend on it).
-  const bool pair = tiling == 2 || (tiling == 0 && M > BM);
+  const Plan pl = tiling == 0 ? auto_plan(M, N, L, max_ctas, ws_bytes, have_ws) : make_plan(tiling, M, N, L, max_ctas);
+  if (pl.scratch_bytes > 0 && (!have_ws || pl.scratch_bytes > ws_bytes)) {
+    char msg[200];
+    snprintf(msg, sizeof(msg),
+             "tbik_gemm: a reduction tree of %d levels needs %zu bytes of scratch for this tiling (got %zu); "
+             "see tbik_gemm_workspace_bytes", L, pl.scratch_bytes, have_ws ? ws_bytes : size_t(0));
+    return set_error(TBIK_ERR_SHAPE, msg);
+  }
+  const Variant& v = kVariants[pl.tiling - 1][pl.deep ? 1 : 0];
+
   CUtensorMap ta, tb;
   int rc = make_tmap(&ta, dtype, A, M, K, lda, BM);
   if (rc != TBIK_OK) return rc;
-  rc = make_tmap(&tb, dtype, W, N, K, ldw, pair ? BN / 2 : BN);
+  rc = make_tmap(&tb, dtype, W, N, K, ldw, v.pair ? v.bn / 2 : v.bn);
   if (rc != TBIK_OK) return rc;
 
   GemmParams p{};
@@ -541,24 +668,17 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
   p.T = T;
   p.F = F;
   p.L = L;
-  const int tile_m = pair ? 2 * BM : BM;
-  p.tiles_m = (M + tile_m - 1) / tile_m;
-  p.tiles_n = (N + BN - 1) / BN;
-  p.group_m = pair ? 4 : 8;
+  p.tiles_m = pl.tiles_m;
+  p.tiles_n = pl.tiles_n;
+  p.group_m = v.pair ? 4 : 8;
+  p.scratch = static_cast<uint32_t*>(workspace);
+  p.scratch_levels = pl.scratch_levels;
   void* status_ptr = nullptr;
   cudaGetSymbolAddress(&status_ptr, g_gemm_status);
   p.status = static_cast<uint32_t*>(status_ptr);
 
-  const int num_tiles = p.tiles_m * p.tiles_n;
-  int ctas = sm_count();
-  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  int units = pair ? ctas / 2 : ctas;
-  if (units < 1) units = 1;
-  if (units > num_tiles) units = num_tiles;
-  const int grid = pair ? 2 * units : units;
-  const bool spill = L > 1 + TMEM_STACK_LEVELS;
-  if (dtype == TBIK_DTYPE_BF16) return launch_variant<__nv_bfloat16>(ta, tb, p, grid, spill, pair, stream);
-  return launch_variant<__half>(ta, tb, p, grid, spill, pair, stream);
+  if (dtype == TBIK_DTYPE_BF16) return launch_variant<__nv_bfloat16>(pl.tiling, pl.deep, ta, tb, p, pl.grid, stream);
+  return launch_variant<__half>(pl.tiling, pl.deep, ta, tb, p, pl.grid, stream);
 }
 
 int gemm_status(uint32_t out[4]) {

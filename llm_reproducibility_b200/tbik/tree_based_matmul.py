@@ -38,6 +38,21 @@ def _k_major_weight(B: torch.Tensor) -> torch.Tensor:
     return Wt.contiguous()
 
 
+_WORKSPACES = {}  # (device index, stream) -> uint8 tensor; scratch for the upper levels of the tree stack
+
+
+def _workspace(device: torch.device, stream: int, nbytes: int) -> Optional[torch.Tensor]:
+    """Scratch buffer for one (device, stream); grown on demand, never shared between streams."""
+    if nbytes == 0:
+        return None
+    key = (device.index, stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
 def matmul_tp_persistent(A: torch.Tensor, B: torch.Tensor, bias: Optional[torch.Tensor] = None,
                          *, leaf: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C = A @ B with the K reduction in the fixed tree order; returns a new [M, N] tensor of A's dtype.
@@ -63,10 +78,13 @@ def matmul_tp_persistent(A: torch.Tensor, B: torch.Tensor, bias: Optional[torch.
     assert C.shape == (M, N) and C.stride(1) == 1 and C.dtype == A.dtype
     with torch.cuda.device(A.device):
         stream = torch.cuda.current_stream().cuda_stream
-        rc = _lib.lib().tbik_gemm(A.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K,
-                                  max(A.stride(0), K), max(W.stride(0), K), max(C.stride(0), N),
-                                  _DTYPE_CODE[A.dtype], leaf, _lib.NODE_INPUT, stream)
-    _lib.check(rc, "tbik_gemm")
+        L = _lib.lib()
+        ws = _workspace(A.device, stream, int(L.tbik_gemm_workspace_bytes(M, N, K, leaf)))
+        rc = L.tbik_gemm_ws(A.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K,
+                            max(A.stride(0), K), max(W.stride(0), K), max(C.stride(0), N),
+                            _DTYPE_CODE[A.dtype], leaf, _lib.NODE_INPUT,
+                            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, stream)
+    _lib.check(rc, "tbik_gemm_ws")
     if bias is not None:
         C += bias
     return C

@@ -81,11 +81,38 @@ def test_deep_trees_use_the_shared_memory_levels(mm, K):
     assert torch.equal(bits(C.cpu()), bits(tbik_matmul_ref(A, B)))
 
 
-def test_tree_deeper_than_supported_is_rejected(mm):
-    A = torch.zeros(8, 65536, dtype=torch.bfloat16, device="cuda")
-    B = torch.zeros(65536, 8, dtype=torch.bfloat16, device="cuda")
-    with pytest.raises(RuntimeError, match="deeper"):
-        mm(A, kmajor(B.cpu()))
+def test_very_deep_tree_needs_scratch():
+    """L = 8 (K = 65536): more levels than fit on chip.  Without scratch the call is refused with a
+    message naming the need; with scratch it runs (levels above the on-chip ones live in L2)."""
+    from llm_reproducibility_b200 import _lib
+    A, B = exact_int_inputs(130, 65536, 136, torch.bfloat16, seed=8, amax=3)
+    Ad, W = A.cuda(), B.cuda().t().contiguous()
+    C = torch.empty(130, 136, dtype=torch.bfloat16, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    rc = _lib.lib().tbik_gemm(Ad.data_ptr(), W.data_ptr(), C.data_ptr(), 130, 136, 65536, 65536, 65536, 136, 0, 256, 0, s)
+    assert rc == -2 and "scratch" in _lib.last_error()
+    ref = tbik_matmul_ref(A, B)
+    for tiling in TILINGS:
+        assert torch.equal(bits(_gemm_ex(Ad, W, 130, 136, 65536, 0, tiling).cpu()), bits(ref)), tiling
+
+
+def test_entry_point_without_scratch_matches_the_one_with_scratch():
+    """tbik_gemm (no scratch, 128x128 tiles) and tbik_gemm_ws (128x256 tiles for M > 128) agree bitwise."""
+    from llm_reproducibility_b200 import _lib
+    from llm_reproducibility_b200.tbik.tree_based_matmul import matmul_tp_persistent
+    L = _lib.lib()
+    M, K, N = 1000, 12288, 1024
+    assert L.tbik_gemm_workspace_bytes(M, N, K, 256) > 0          # (3,5) tree: two levels go to scratch
+    assert L.tbik_gemm_workspace_bytes(64, N, K, 256) == 0        # small M: no scratch needed
+    g = torch.Generator(device="cuda").manual_seed(1)
+    A = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    W = (torch.randn(N, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    C0 = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    assert L.tbik_gemm(A.data_ptr(), W.data_ptr(), C0.data_ptr(), M, N, K, K, K, N, 0, 256, 0,
+                       torch.cuda.current_stream().cuda_stream) == 0
+    C1 = matmul_tp_persistent(A, W.t())
+    torch.cuda.synchronize()
+    assert torch.equal(bits(C0), bits(C1))
 
 
 @pytest.mark.parametrize("leaf,K", [(128, 3200), (64, 1600), (640, 3200), (512, 4096)])
@@ -152,18 +179,30 @@ def test_full_size_invariance_properties(mm, K, N):
     assert rel < MAX_REL_ERR_VS_FP64
 
 
-def _gemm_ex(Ad, W, M, N, K, ctas, tiling, dtype_code=0, leaf=256):
+_WS = {}
+
+
+def _gemm_ex(Ad, W, M, N, K, ctas, tiling, dtype_code=0, leaf=256, workspace=True):
     from llm_reproducibility_b200 import _lib
     C = torch.empty(M, N, dtype=Ad.dtype, device="cuda")
+    if workspace:
+        if "ws" not in _WS:
+            _WS["ws"] = torch.empty(64 << 20, dtype=torch.uint8, device="cuda")
+        wp, wn = _WS["ws"].data_ptr(), _WS["ws"].numel()
+    else:
+        wp, wn = None, 0
     rc = _lib.lib().tbik_gemm_ex(Ad.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K, K, K, N,
-                                 dtype_code, leaf, _lib.NODE_INPUT, ctas, tiling,
+                                 dtype_code, leaf, _lib.NODE_INPUT, ctas, tiling, wp, wn,
                                  torch.cuda.current_stream().cuda_stream)
     assert rc == 0, _lib.last_error()
     torch.cuda.synchronize()
     return C
 
 
-@pytest.mark.parametrize("tiling", [1, 2])
+TILINGS = [1, 2, 3, 4]
+
+
+@pytest.mark.parametrize("tiling", TILINGS)
 def test_result_does_not_depend_on_cta_count(tiling):
     A, B = normal_inputs(700, 1536, 520, torch.bfloat16, seed=5)
     Ad, W = A.cuda(), B.cuda().t().contiguous()
@@ -174,21 +213,24 @@ def test_result_does_not_depend_on_cta_count(tiling):
 
 @pytest.mark.parametrize("M,K,N", [(1, 4096, 512), (100, 4096, 512), (128, 12288, 256), (129, 4096, 384),
                                    (700, 1536, 520), (2048, 4096, 4096), (4096, 12288, 1024)])
-def test_single_cta_and_cta_pair_tilings_agree_bitwise(M, K, N):
-    """Random (not exactly representable) operands: the 128x128 one-CTA schedule and the 256x128
-    CTA-pair schedule must give the same bits, otherwise results would change with the batch size."""
+def test_all_tilings_agree_bitwise(M, K, N):
+    """Random (not exactly representable) operands: the 128x128, 256x128 (CTA pair), 128x256 and
+    256x256 (CTA pair) schedules must give the same bits, otherwise results would change with the
+    batch size (the automatic choice depends on M)."""
     g = torch.Generator(device="cuda").manual_seed(M + K + N)
     A = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
     W = (torch.randn(N, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
     one = _gemm_ex(A, W, M, N, K, 0, 1)
-    two = _gemm_ex(A, W, M, N, K, 0, 2)
-    assert torch.equal(bits(one), bits(two))
+    for tiling in TILINGS[1:]:
+        assert torch.equal(bits(one), bits(_gemm_ex(A, W, M, N, K, 0, tiling))), tiling
     h = torch.randn(M, K, generator=g, device="cuda").to(torch.float16)
     Wh = W.to(torch.float16)
-    assert torch.equal(bits(_gemm_ex(h, Wh, M, N, K, 0, 1, dtype_code=1)), bits(_gemm_ex(h, Wh, M, N, K, 0, 2, dtype_code=1)))
+    one = _gemm_ex(h, Wh, M, N, K, 0, 1, dtype_code=1)
+    for tiling in TILINGS[1:]:
+        assert torch.equal(bits(one), bits(_gemm_ex(h, Wh, M, N, K, 0, tiling, dtype_code=1))), tiling
 
 
-@pytest.mark.parametrize("tiling", [1, 2])
+@pytest.mark.parametrize("tiling", TILINGS)
 @pytest.mark.parametrize("M,K,N", [(300, 12288, 384), (130, 12800, 128), (130, 16384, 136), (257, 768, 136)])
 def test_both_tilings_bit_exact_vs_oracle(tiling, M, K, N):
     A, B = exact_int_inputs(M, K, N, torch.bfloat16, seed=M + K, amax=7)
