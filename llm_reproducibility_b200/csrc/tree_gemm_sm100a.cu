@@ -287,38 +287,44 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // "accumulator drained" goes to the UMMA issuer, which lives in the leader CTA
     const uint32_t tempty0 = PAIR ? map_to_cta(tempty_bar(0), 0) : tempty_bar(0);
 
-    // One 32-column chunk (16 packed words) of stack level `lvl` (>= 1) of this thread.
-    auto stack_load = [&](int lvl, int c, uint32_t (&t)[16]) {
+    constexpr int NW = NCH * (CHUNK / 2);  // packed words of one stack level held by one thread
+    // Stack level `lvl` (>= 1) of this thread: all NW words at once, so that one memory latency
+    // is paid per level, not per chunk.
+    auto stack_load = [&](int lvl, uint32_t (&t)[NW]) {
       const int idx = lvl - 1;
       if (idx < C_::TMEM_LEVELS) {
-        tmem_ld16(tmem_base + lane_off + C_::TMEM_STACK_COL0 + idx * (BN / 2) + h * (BN / 4) + c * 16, t);
+        const uint32_t col = tmem_base + lane_off + C_::TMEM_STACK_COL0 + idx * (BN / 2) + h * (BN / 4);
+#pragma unroll
+        for (int w = 0; w < NW / 32; ++w) tmem_ld32(col + w * 32, *reinterpret_cast<uint32_t(*)[32]>(&t[w * 32]));
         tmem_wait_ld();
       } else if (idx < C_::TMEM_LEVELS + SLEVELS) {
-        const uint32_t* sp = smem_stack + ((idx - C_::TMEM_LEVELS) * NCH + c) * 16 * EPI_THREADS + epi_tid;
+        const uint32_t* sp = smem_stack + (idx - C_::TMEM_LEVELS) * C_::LEVEL_WORDS + epi_tid;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) t[j] = sp[j * EPI_THREADS];
+        for (int w = 0; w < NW; ++w) t[w] = sp[w * EPI_THREADS];
       } else {
-        const uint32_t* gp = gl_stack + ((idx - C_::TMEM_LEVELS - SLEVELS) * NCH + c) * 16 * EPI_THREADS + epi_tid;
+        const uint32_t* gp = gl_stack + (idx - C_::TMEM_LEVELS - SLEVELS) * C_::LEVEL_WORDS + epi_tid;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) t[j] = gp[j * EPI_THREADS];
+        for (int w = 0; w < NW; ++w) t[w] = gp[w * EPI_THREADS];
       }
     };
-    auto stack_store = [&](int lvl, int c, const uint32_t (&v)[16]) {
+    auto stack_store = [&](int lvl, const uint32_t (&v)[NW]) {
       const int idx = lvl - 1;
       if (idx < C_::TMEM_LEVELS) {
-        tmem_st16(tmem_base + lane_off + C_::TMEM_STACK_COL0 + idx * (BN / 2) + h * (BN / 4) + c * 16, v);
+        const uint32_t col = tmem_base + lane_off + C_::TMEM_STACK_COL0 + idx * (BN / 2) + h * (BN / 4);
+#pragma unroll
+        for (int w = 0; w < NW / 32; ++w) tmem_st32(col + w * 32, *reinterpret_cast<const uint32_t(*)[32]>(&v[w * 32]));
       } else if (idx < C_::TMEM_LEVELS + SLEVELS) {
-        uint32_t* sp = smem_stack + ((idx - C_::TMEM_LEVELS) * NCH + c) * 16 * EPI_THREADS + epi_tid;
+        uint32_t* sp = smem_stack + (idx - C_::TMEM_LEVELS) * C_::LEVEL_WORDS + epi_tid;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) sp[j * EPI_THREADS] = v[j];
+        for (int w = 0; w < NW; ++w) sp[w * EPI_THREADS] = v[w];
       } else {
-        uint32_t* gp = gl_stack + ((idx - C_::TMEM_LEVELS - SLEVELS) * NCH + c) * 16 * EPI_THREADS + epi_tid;
+        uint32_t* gp = gl_stack + (idx - C_::TMEM_LEVELS - SLEVELS) * C_::LEVEL_WORDS + epi_tid;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) gp[j * EPI_THREADS] = v[j];
+        for (int w = 0; w < NW; ++w) gp[w * EPI_THREADS] = v[w];
       }
     };
 
-    uint32_t s0[NCH][16];  // open level-0 group
+    uint32_t s0[NW];  // the open level-0 group; once it closes, the node that climbs the tree
     uint32_t leaf_ctr = 0;
     bool ok = true;
     for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
@@ -340,70 +346,62 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if constexpr (C_::TMEM_LEVELS > 0) tmem_wait_st();  // stack stores of earlier leaves have landed
         const uint32_t tacc = tmem_base + lane_off + a * BN + h * C_::COLS_PER_WARP;
         const bool add0 = c0 > 0;
-        const bool close = c0 + 1 == p.F;
-        uint32_t raw[2][32];
-        tmem_ld32(tacc, raw[0]);
+        {
+          // drain the accumulator chunk by chunk; the next chunk flies while this one is rounded and added
+          uint32_t raw[2][32];
+          tmem_ld32(tacc, raw[0]);
 #pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-          tmem_wait_ld();
-          if (c + 1 < NCH) {
-            tmem_ld32(tacc + (c + 1) * CHUNK, raw[(c + 1) & 1]);  // next chunk flies while this one is combined
-          } else {
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * a);  // accumulator may be overwritten now
-          }
-          uint32_t cur[16];
+          for (int c = 0; c < NCH; ++c) {
+            tmem_wait_ld();
+            if (c + 1 < NCH) {
+              tmem_ld32(tacc + (c + 1) * CHUNK, raw[(c + 1) & 1]);
+            } else {
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * a);  // accumulator may be overwritten now
+            }
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            cur[j] = Pack16<T>::from_f32(__uint_as_float(raw[c & 1][2 * j]), __uint_as_float(raw[c & 1][2 * j + 1]));
-          // level 0: radix F, sequential
-          if (add0) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) cur[j] = Pack16<T>::add(s0[c][j], cur[j]);
-          }
-          if (!close) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) s0[c][j] = cur[j];
-            continue;
-          }
-          // levels >= 1: binary counter over finished groups
-          uint32_t gb = g;
-          int lvl = 1;
-          while (lvl < p.L && (gb & 1u)) {
-            uint32_t t[16];
-            stack_load(lvl, c, t);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) cur[j] = Pack16<T>::add(t[j], cur[j]);
-            gb >>= 1;
-            ++lvl;
-          }
-          if (lvl < p.L) {
-            stack_store(lvl, c, cur);
-          } else {
-            // root of the tile's tree: write 32 columns of C
-            const int col0 = tn * BN + h * C_::COLS_PER_WARP + c * CHUNK;
-            if (row < p.M && col0 < p.N) {
-              if (vec_ok && col0 + CHUNK <= p.N) {
-                uint4* dst = reinterpret_cast<uint4*>(crow + col0);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) dst[j] = make_uint4(cur[4 * j], cur[4 * j + 1], cur[4 * j + 2], cur[4 * j + 3]);
-              } else {
-                uint16_t* dst = reinterpret_cast<uint16_t*>(crow + col0);
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  if (col0 + 2 * j < p.N) dst[2 * j] = static_cast<uint16_t>(cur[j] & 0xFFFFu);
-                  if (col0 + 2 * j + 1 < p.N) dst[2 * j + 1] = static_cast<uint16_t>(cur[j] >> 16);
-                }
-              }
+            for (int j = 0; j < 16; ++j) {
+              const uint32_t v = Pack16<T>::from_f32(__uint_as_float(raw[c & 1][2 * j]), __uint_as_float(raw[c & 1][2 * j + 1]));
+              s0[c * 16 + j] = add0 ? Pack16<T>::add(s0[c * 16 + j], v) : v;  // level 0: radix F, sequential
             }
           }
         }
-        if (close) {
-          c0 = 0;
-          ++g;
-        } else {
-          ++c0;
+        if (++c0 < p.F) continue;
+        c0 = 0;
+        // levels >= 1: binary counter over finished groups
+        uint32_t gb = g++;
+        int lvl = 1;
+        while (lvl < p.L && (gb & 1u)) {
+          uint32_t t[NW];
+          stack_load(lvl, t);
+#pragma unroll
+          for (int w = 0; w < NW; ++w) s0[w] = Pack16<T>::add(t[w], s0[w]);
+          gb >>= 1;
+          ++lvl;
+        }
+        if (lvl < p.L) {
+          stack_store(lvl, s0);
+        } else if (row < p.M) {
+          // root of the tile's tree: write this thread's BN/2 columns of C
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) {
+            const int col0 = tn * BN + h * C_::COLS_PER_WARP + c * CHUNK;
+            if (col0 >= p.N) continue;
+            if (vec_ok && col0 + CHUNK <= p.N) {
+              uint4* dst = reinterpret_cast<uint4*>(crow + col0);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                dst[j] = make_uint4(s0[c * 16 + 4 * j], s0[c * 16 + 4 * j + 1], s0[c * 16 + 4 * j + 2], s0[c * 16 + 4 * j + 3]);
+            } else {
+              uint16_t* dst = reinterpret_cast<uint16_t*>(crow + col0);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (col0 + 2 * j < p.N) dst[2 * j] = static_cast<uint16_t>(s0[c * 16 + j] & 0xFFFFu);
+                if (col0 + 2 * j + 1 < p.N) dst[2 * j + 1] = static_cast<uint16_t>(s0[c * 16 + j] >> 16);
+              }
+            }
+          }
         }
       }
     }
