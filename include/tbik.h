@@ -88,7 +88,8 @@ int tbik_gemm_ex(const void* A, const void* W, void* C, int M, int N, int K, int
 
 /* Reads (and clears) the device-side status of the GEMM kernels on the current device:
  * out[0] != 0 means a kernel gave up on a bounded wait (out[1] = block, out[2] = role).
- * Synchronises with the device.  No counterpart in the reference (its waits are unbounded). */
+ * out[3] = SM clock cycles CTA 0 of the most recent launch spent in its main loop (for utilisation
+ * figures that do not depend on the clock the GPU happened to run at).  Synchronises with the device.  No counterpart in the reference (its waits are unbounded). */
 int tbik_gemm_status(uint32_t out[4]);
 
 /* ---- cross-GPU all-reduce over IPC-registered buffers --------------------------------------- */

@@ -60,7 +60,7 @@ struct GemmParams {
   int tiles_m, tiles_n, group_m;  // tiles_m counts 128-row (single) or 256-row (pair) tiles
   uint32_t* scratch;     // global stack levels: [cta][level][chunk][word][epilogue thread]
   int scratch_levels;    // levels per CTA held in `scratch`
-  uint32_t* status;      // [0] error code, [1] block, [2] role
+  uint32_t* status;      // [0] error code, [1] block, [2] role, [3] SM cycles of block 0 (last launch)
 };
 
 // Static shape of one kernel variant.
@@ -160,6 +160,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const uint32_t tmem_base = *tmem_ptr_smem;
 
   int role_failed = 0;  // which role observed the abort (for the status word)
+  const long long cycles0 = clock64();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (every CTA)
@@ -417,6 +418,8 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       p.status[2] = static_cast<uint32_t>(role_failed);
     }
   }
+  if (blockIdx.x == 0 && threadIdx.x == 0 && p.status != nullptr)
+    p.status[3] = static_cast<uint32_t>(clock64() - cycles0);  // SM cycles block 0 spent in the main loop
   if (warp == 2) {
     tc_fence_after_sync();
     if constexpr (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS); else tmem_dealloc(tmem_base, TMEM_COLS);
@@ -522,7 +525,7 @@ constexpr Variant kVariants[4][2] = {
     {variant_of<128, 6, 0, false>(), variant_of<128, 4, 2, false>()},
     {variant_of<128, 8, 0, true>(), variant_of<128, 5, 2, true>()},
     {variant_of<256, 3, 1, false>(), variant_of<256, 3, 1, false>()},
-    {variant_of<256, 3, 2, true>(), variant_of<256, 3, 2, true>()},
+    {variant_of<256, 5, 1, true>(), variant_of<256, 5, 1, true>()},
 };
 
 template <typename T>
@@ -532,7 +535,7 @@ int launch_variant(int tiling, bool deep, const CUtensorMap& ta, const CUtensorM
     case 1: return deep ? launch<T, 128, 4, 2, false>(ta, tb, p, grid, stream) : launch<T, 128, 6, 0, false>(ta, tb, p, grid, stream);
     case 2: return deep ? launch<T, 128, 5, 2, true>(ta, tb, p, grid, stream) : launch<T, 128, 8, 0, true>(ta, tb, p, grid, stream);
     case 3: return launch<T, 256, 3, 1, false>(ta, tb, p, grid, stream);
-    case 4: return launch<T, 256, 3, 2, true>(ta, tb, p, grid, stream);
+    case 4: return launch<T, 256, 5, 1, true>(ta, tb, p, grid, stream);
     default: return set_error(TBIK_ERR_ARG, "unknown tiling");
   }
 }
