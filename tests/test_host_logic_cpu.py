@@ -153,3 +153,29 @@ def test_native_tree_sum_rejects_non_power_of_two_world():
 @pytest.mark.parametrize("world", [2, 4])
 def test_row_parallel_forward_on_gloo_ranks(world):
     assert all(run_ranks(hw.row_parallel_layer, world, backend="gloo"))
+
+
+def test_install_aliases_gives_the_reference_import_names():
+    import subprocess
+    code = ("import sys; sys.path.insert(0, %r); import llm_reproducibility_b200 as p; p.install_aliases();"
+            "from src.tbik.tree_based_matmul import matmul_tp_persistent;"
+            "from tbik.tree_based_all_reduce import tree_all_reduce_sum, tree_all_reduce_sum_native;"
+            "from mini_allreduce import CustomAllreduce, CustomTreeAllreduce;"
+            "import mini_allreduce.custom_all_reduce_ops as ops; import tbik_kernel.allreduce;"
+            "from src.patch import apply_patches; from src.utils import tp_invariant_is_enabled;"
+            "assert ops.meta_size() > 0; print('ok')") % ROOT
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True)
+    assert out.returncode == 0 and "ok" in out.stdout, out.stderr
+
+
+def test_patch_binds_to_installed_vllm():
+    """The row-parallel patch must import against the vLLM in this image (0.22) and replace forward."""
+    import subprocess
+    code = ("import sys; sys.path.insert(0, %r);"
+            "from llm_reproducibility_b200.patch.patch_tp_invariant import patch_row_linear;"
+            "from vllm.model_executor.layers.linear import RowParallelLinear as R; old = R.forward;"
+            "patch_row_linear(); assert R.forward is not old; print('ok')") % ROOT
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    if "No module named 'vllm'" in out.stderr:
+        pytest.skip("vllm not installed")
+    assert out.returncode == 0 and "ok" in out.stdout, out.stderr[-2000:]
