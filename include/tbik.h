@@ -86,6 +86,26 @@ int tbik_gemm_ex(const void* A, const void* W, void* C, int M, int N, int K, int
                  int dtype, int leaf, int node_dtype, int max_ctas, int tiling, void* workspace,
                  size_t workspace_bytes, tbik_stream_t stream);
 
+/* tbik_gemm_ws for callers that have no way to hand over device memory of their own: a host
+ * runtime that binds this C ABI without a device allocator, or a serving engine that has already
+ * given all free HBM to its KV cache, where a cudaMalloc at this point would fail or stall.  The
+ * scratch is a fixed array inside the library image (tbik_gemm_static_scratch_bytes() bytes, 32 MiB;
+ * each GPU that loads the library keeps it until the process exits).  The call performs no
+ * allocation of any kind.  Sizes whose scratch need (tbik_gemm_workspace_bytes) exceeds the array
+ * are refused with TBIK_ERR_SHAPE and a message naming both numbers.  Same bits as tbik_gemm_ws.
+ * The first call on each device looks up the array's device address; make that first call outside
+ * any stream capture.  All calls on a device share the one array, so two calls that can overlap on
+ * the GPU (different streams) race on it -- serialise them.  The array keeps whatever the previous
+ * call left behind; nothing in it needs clearing, because every word is written before it is read
+ * within a call.
+ * This entry point has no counterpart in the reference. */
+int tbik_gemm_static(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
+                     int dtype, int leaf, int node_dtype, tbik_stream_t stream);
+
+/* Capacity in bytes of the scratch built into the library for tbik_gemm_static.
+ * No counterpart in the reference. */
+size_t tbik_gemm_static_scratch_bytes(void);
+
 /* Reads (and clears) the device-side status of the GEMM kernels on the current device:
  * out[0] != 0 means a kernel gave up on a bounded wait (out[1] = block, out[2] = role).
  * out[3] = SM clock cycles CTA 0 of the most recent launch spent in its main loop (for utilisation

@@ -54,6 +54,14 @@ int tbik_gemm_ex(const void* A, const void* W, void* C, int M, int N, int K, int
                            workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
+size_t tbik_gemm_static_scratch_bytes(void) { return tbik::gemm_static_scratch_bytes(); }
+
+int tbik_gemm_static(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
+                     int dtype, int leaf, int node_dtype, tbik_stream_t stream) {
+  return tbik::gemm_launch_static(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype,
+                                  static_cast<cudaStream_t>(stream));
+}
+
 int tbik_gemm_status(uint32_t out[4]) {
   if (!out) return tbik::set_error(TBIK_ERR_ARG, "tbik_gemm_status: null output pointer");
   return tbik::gemm_status(out);

@@ -17,6 +17,9 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
                 int dtype, int leaf, int node_dtype, int max_ctas, int tiling, void* workspace, size_t ws_bytes,
                 cudaStream_t stream);
 size_t gemm_workspace_bytes(int M, int N, int64_t K, int leaf);
+size_t gemm_static_scratch_bytes();
+int gemm_launch_static(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw,
+                       int64_t ldc, int dtype, int leaf, int node_dtype, cudaStream_t stream);
 int gemm_status(uint32_t out[4]);
 
 

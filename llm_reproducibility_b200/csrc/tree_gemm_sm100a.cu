@@ -682,6 +682,42 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
   return launch_variant<__half>(pl.tiling, pl.deep, ta, tb, p, pl.grid, stream);
 }
 
+// ---------------------------------------------------------------- the entry point that allocates nothing
+// Scratch for the upper stack levels, built into the library image: every GPU that loads the library
+// holds these bytes until the process exits.  32 MiB covers the 128x256 tiling of every Qwen3-8B
+// row-split layer (down_proj, 5 tree levels: 148 CTAs x 3 levels x 64 KiB = 27.75 MiB).
+constexpr size_t kStaticScratchBytes = size_t(32) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+size_t gemm_static_scratch_bytes() { return kStaticScratchBytes; }
+
+int gemm_launch_static(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw,
+                       int64_t ldc, int dtype, int leaf, int node_dtype, cudaStream_t stream) {
+  // In host code `g_static_scratch` is only a handle for the runtime, not a device address: the address
+  // the kernel may use has to be asked for, once per device, with that device current.
+  static void* device_addr[64] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return set_cuda_error(e, "cudaGetDevice");
+  if (dev < 0 || dev >= 64) return set_error(TBIK_ERR_ARG, "tbik_gemm_static: device index out of range");
+  if (device_addr[dev] == nullptr) {
+    void* addr = nullptr;
+    e = cudaGetSymbolAddress(&addr, g_static_scratch);
+    if (e != cudaSuccess || addr == nullptr) return set_cuda_error(e, "cudaGetSymbolAddress(g_static_scratch)");
+    device_addr[dev] = addr;
+  }
+  const size_t need = gemm_workspace_bytes(M, N, K, leaf);
+  if (need > kStaticScratchBytes) {
+    char msg[200];
+    snprintf(msg, sizeof(msg),
+             "tbik_gemm_static: these sizes need %zu bytes of scratch, more than the %zu bytes built into the "
+             "library; use tbik_gemm_ws with a caller-owned buffer", need, kStaticScratchBytes);
+    return set_error(TBIK_ERR_SHAPE, msg);
+  }
+  return gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, 0, 0, device_addr[dev],
+                     kStaticScratchBytes, stream);
+}
+
 int gemm_status(uint32_t out[4]) {
   cudaError_t e = cudaMemcpyFromSymbol(out, g_gemm_status, sizeof(uint32_t) * 4);
   if (e != cudaSuccess) return set_cuda_error(e, "cudaMemcpyFromSymbol(g_gemm_status)");

@@ -1,0 +1,65 @@
+"""`tbik_gemm_static`: the GEMM entry point for callers that cannot allocate device memory.
+
+Some hosts of this library have no device allocator to offer (a C / Go / Rust service binding the
+C ABI directly) or must not call one at the point of use (an inference server that has handed every
+free byte of HBM to its KV cache).  For them the library carries its own fixed scratch array.  This
+test calls the entry point through the C ABI twice in a row, on different operands, and requires
+the result to equal -- bit for bit, the tolerance of every other integer-exactness test here --
+what `tbik_gemm_ws` returns with a caller-owned scratch buffer.  It also checks that a size whose
+scratch need exceeds the built-in array is refused before anything is launched.
+The file name sorts last so that a failure here cannot hide the other tests in a `-x` run.
+"""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _bits(t):
+    return t.contiguous().view(torch.int16)
+
+
+def _run(fn, A, W, extra=()):
+    from llm_reproducibility_b200 import _lib
+    M, K = A.shape
+    N = W.shape[0]
+    C = torch.empty(M, N, dtype=A.dtype, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    rc = fn(A.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K, K, K, N, _lib.DTYPE_BF16, 256, _lib.NODE_INPUT, *extra, s)
+    assert rc == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    return C
+
+
+def test_static_scratch_entry_point_matches_workspace_entry_point_twice():
+    from llm_reproducibility_b200 import _lib
+    L = _lib.lib()
+    M, K, N = 1000, 12288, 1024           # 5-level tree: the 128x256 tiling keeps 3 levels in scratch
+    need = L.tbik_gemm_workspace_bytes(M, N, K, 256)
+    assert 0 < need <= L.tbik_gemm_static_scratch_bytes()
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(2024)
+    for call in range(2):                  # second call: new operands, scratch still holds the first call's words
+        A = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+        W = (torch.randn(N, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+        want = _run(L.tbik_gemm_ws, A, W, extra=(ws.data_ptr(), ws.numel()))
+        got = _run(L.tbik_gemm_static, A, W)
+        assert torch.equal(_bits(got), _bits(want)), f"call {call}"
+    st = (ctypes.c_uint32 * 4)()
+    assert L.tbik_gemm_status(st) == 0 and st[0] == 0
+
+
+def test_static_scratch_entry_point_refuses_sizes_beyond_its_array():
+    from llm_reproducibility_b200 import _lib
+    L = _lib.lib()
+    M, K, N = 8192, 65536, 768            # 8-level tree on 148 CTAs: 6 levels x 64 KiB x 148 > 32 MiB
+    assert L.tbik_gemm_workspace_bytes(M, N, K, 256) > L.tbik_gemm_static_scratch_bytes()
+    x = torch.zeros(4096, dtype=torch.bfloat16, device="cuda")   # never dereferenced: the call is refused first
+    rc = L.tbik_gemm_static(x.data_ptr(), x.data_ptr(), x.data_ptr(), M, N, K, K, K, N, _lib.DTYPE_BF16, 256,
+                            _lib.NODE_INPUT, torch.cuda.current_stream().cuda_stream)
+    assert rc == -2
+    msg = _lib.last_error()
+    assert "built into the library" in msg and "tbik_gemm_ws" in msg
+    torch.cuda.synchronize()
