@@ -185,7 +185,7 @@ def main():
         return
 
     import torch.distributed as dist
-    from llm_reproducibility_b200.tbik.tree_based_all_reduce import reset_communicator, tree_all_reduce_sum
+    from llm_reproducibility_b200.tbik.tree_based_all_reduce import reset_communicator, tree_matmul_all_reduce
     from llm_reproducibility_b200.tbik.tree_based_matmul import gemm_device_status, matmul_tp_persistent
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -215,9 +215,10 @@ def main():
 
     def step(i):
         for X, W, C in sets[i % nsets]:
-            out = matmul_tp_persistent(X, W.t(), out=C)
             if tp > 1:
-                out = tree_all_reduce_sum(out, None)
+                out = tree_matmul_all_reduce(X, W.t(), None)
+            else:
+                out = matmul_tp_persistent(X, W.t(), out=C)
         return out
 
     def sync_all():
@@ -271,9 +272,10 @@ def main():
     def e2e_step(i):
         for li, (X, W, C) in enumerate(sets[i % nsets]):
             dev_in[li].copy_(host_in[li], non_blocking=True)
-            out = matmul_tp_persistent(dev_in[li], W.t(), out=C)
             if tp > 1:
-                out = tree_all_reduce_sum(out, None)
+                out = tree_matmul_all_reduce(dev_in[li], W.t(), None)
+            else:
+                out = matmul_tp_persistent(dev_in[li], W.t(), out=C)
             host_out[li].copy_(out, non_blocking=True)
     for i in range(3):
         e2e_step(i)

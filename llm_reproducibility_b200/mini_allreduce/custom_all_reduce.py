@@ -181,6 +181,28 @@ class CustomAllreduce:
             self._native_all_reduce(self._ptr, inp, out, self.buffer_ptrs[self.rank], self.max_size)
         return out
 
+    def registered_view(self, shape, dtype: torch.dtype) -> Optional[torch.Tensor]:
+        """A tensor that aliases the start of this rank's IPC-registered data buffer, or None if it
+        does not fit.  A producer (the row-split GEMM) can write its partial result straight into it
+        and call `all_reduce(view, registered=True)`: the staging copy of the reference
+        (custom_all_reduce.cu:112-114) disappears.  The view is only valid until the next all-reduce
+        through this object has been enqueued."""
+        if self.disabled or self.device.type != "cuda":
+            return None
+        numel = 1
+        for d in shape:
+            numel *= int(d)
+        nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+        if nbytes == 0 or nbytes % 16 != 0 or nbytes >= self.max_size:
+            return None
+
+        class _Raw:
+            __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "version": 2,
+                                        "data": (self.buffer_ptrs[self.rank], False)}
+
+        flat = torch.as_tensor(_Raw(), device=self.device)
+        return flat.view(dtype).view(*shape)
+
     def _dispatch(self, input: torch.Tensor) -> Optional[torch.Tensor]:
         if self.disabled or not self.should_custom_ar(input):
             return None

@@ -10,7 +10,7 @@ from typing import Callable, Optional
 
 import torch
 
-from ..tbik.tree_based_all_reduce import tree_all_reduce_sum
+from ..tbik.tree_based_all_reduce import tree_matmul_all_reduce
 from ..tbik.tree_based_matmul import matmul_tp_persistent
 
 
@@ -34,13 +34,11 @@ def row_parallel_forward(self, input_, *, device_group_fn: Optional[Callable] = 
     # the bias is added once, after the reduction, and only where it is not skipped
     lead = input_parallel.shape[:-1]
     x2d = input_parallel.reshape(-1, input_parallel.shape[-1])
-    output_parallel = matmul_tp_persistent(x2d, self.weight.t())
-
     if self.reduce_results and self.tp_size > 1:
         group = device_group_fn() if device_group_fn is not None else None
-        output = tree_all_reduce_sum(output_parallel, device_group=group)
+        output = tree_matmul_all_reduce(x2d, self.weight.t(), group)
     else:
-        output = output_parallel
+        output = matmul_tp_persistent(x2d, self.weight.t())
     output = output.reshape(*lead, output.shape[-1])
 
     if (not self.skip_bias_add) and self.bias is not None:

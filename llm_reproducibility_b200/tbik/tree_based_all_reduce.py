@@ -37,6 +37,27 @@ def tree_all_reduce_sum(x: torch.Tensor, device_group=None) -> torch.Tensor:
     return y
 
 
+def tree_matmul_all_reduce(A: torch.Tensor, B: torch.Tensor, device_group=None) -> torch.Tensor:
+    """Row-split layer in one call: this rank's tree matmul, then the tree all-reduce.
+
+    Same bits as `tree_all_reduce_sum(matmul_tp_persistent(A, B), group)`.  When the peer-to-peer
+    communicator is usable the GEMM writes its partial result directly into the IPC-registered
+    buffer the peers read from, so no staging copy is made."""
+    global custom_ar
+    from .tree_based_matmul import matmul_tp_persistent
+    if custom_ar is None:
+        from ..mini_allreduce import CustomTreeAllreduce
+        custom_ar = CustomTreeAllreduce(group=device_group, device=A.device, max_size=_max_size())
+    view = None
+    capturing = A.is_cuda and torch.cuda.is_current_stream_capturing()
+    if not custom_ar.disabled and not custom_ar._IS_CAPTURING and not capturing:
+        view = custom_ar.registered_view((A.shape[0], B.shape[1]), A.dtype)
+    if view is None:
+        return tree_all_reduce_sum(matmul_tp_persistent(A, B), device_group)
+    matmul_tp_persistent(A, B, out=view)
+    return custom_ar.all_reduce(view, registered=True)
+
+
 def tree_all_reduce_sum_native(x: torch.Tensor, device_group=None) -> torch.Tensor:
     """all_gather, then pairwise in-place adds in tree order (library collective; the comparator)."""
     world_size = dist.get_world_size(device_group)

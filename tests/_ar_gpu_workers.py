@@ -148,6 +148,21 @@ def dispatcher(rank, world):
     full = matmul_tp_persistent(X, W.t())
     torch.cuda.synchronize()
     assert torch.equal(bits(out), bits(full)), "TP result differs from the single-device result"
+    # the un-fused composition gives the same bits, repeatedly (the registered buffer is reused)
+    for _ in range(3):
+        part = matmul_tp_persistent(X[:, rank * ks:(rank + 1) * ks], Layer.weight.t())
+        assert torch.equal(bits(tar.tree_all_reduce_sum(part, None)), bits(full))
+        assert torch.equal(bits(tar.tree_matmul_all_reduce(X[:, rank * ks:(rank + 1) * ks], Layer.weight.t(), None)), bits(full))
+    # Qwen3-8B shapes at M = 2048 (two-shot schedule, 16 MiB message)
+    g2 = torch.Generator(device=device).manual_seed(99)
+    for (K2, N2) in ((4096, 4096), (12288, 4096)):
+        X2 = torch.randn(2048, K2, generator=g2, device=device).to(torch.bfloat16)
+        W2 = (torch.randn(N2, K2, generator=g2, device=device) * 0.02).to(torch.bfloat16)
+        k2 = K2 // world
+        got = tar.tree_matmul_all_reduce(X2[:, rank * k2:(rank + 1) * k2], W2[:, rank * k2:(rank + 1) * k2].t(), None)
+        want = matmul_tp_persistent(X2, W2.t())
+        torch.cuda.synchronize()
+        assert torch.equal(bits(got), bits(want)), (K2, N2)
     dist.barrier()
     tar.reset_communicator()
     return True

@@ -151,7 +151,16 @@ def row_parallel_layer(rank, world):
     from oracle.tbik_ref import exact_int_inputs, tbik_matmul_ref
 
     fake_backend.install(car, dist.group.WORLD, hostname="same")
-    pti.matmul_tp_persistent = lambda a, b: tbik_matmul_ref(a, b)
+    import llm_reproducibility_b200.tbik.tree_based_matmul as tbm
+
+    def fake_matmul(a, b, bias=None, out=None, **kw):
+        c = tbik_matmul_ref(a, b)
+        if out is not None:
+            out.copy_(c)
+            return out
+        return c
+    pti.matmul_tp_persistent = fake_matmul
+    tbm.matmul_tp_persistent = fake_matmul
     try:
         M, K, N = 6, 2048, 64
         A, B = exact_int_inputs(M, K, N, torch.bfloat16, seed=5, amax=7)
