@@ -113,6 +113,21 @@ TBIK_DEVICE void tma_load_2d(uint32_t smem_dst, const void* tmap, int32_t x, int
       : "memory");
 }
 
+
+// Tiled store shared memory -> global through the TMA unit (bulk async-group completion).
+TBIK_DEVICE void tma_store_2d(const void* tmap, uint32_t smem_src, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_src), "r"(x), "r"(y)
+               : "memory");
+}
+TBIK_DEVICE void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// All bulk stores committed by this thread have finished READING shared memory.
+TBIK_DEVICE void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Named barrier over `count` threads (a multiple of 32), separate from __syncthreads' barrier 0.
+TBIK_DEVICE void named_barrier_sync(uint32_t id, uint32_t count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05 / TMEM
 TBIK_DEVICE void tmem_alloc(uint32_t smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols)

@@ -60,6 +60,7 @@ struct GemmParams {
   int tiles_m, tiles_n, group_m;  // tiles_m counts 128-row (single) or 256-row (pair) tiles
   uint32_t* scratch;     // global stack levels: [cta][level][chunk][word][epilogue thread]
   int scratch_levels;    // levels per CTA held in `scratch`
+  int tma_store;         // 1: write C with TMA stores staged in the shared-memory stack slot (tmap_c valid)
   uint32_t* status;      // [0] error code, [1] block, [2] role, [3] SM cycles of block 0 (last launch)
 };
 
@@ -81,7 +82,8 @@ struct Cfg {
   static constexpr uint32_t OFF_EMPTY = OFF_FULL + 8 * STAGES;
   static constexpr uint32_t OFF_TFULL = OFF_EMPTY + 8 * STAGES;
   static constexpr uint32_t OFF_TEMPTY = OFF_TFULL + 16;
-  static constexpr uint32_t OFF_TMEM_PTR = OFF_TEMPTY + 16;
+  static constexpr uint32_t OFF_EPI_BAR = OFF_TEMPTY + 16;   // rendezvous of the 8 epilogue warps
+  static constexpr uint32_t OFF_TMEM_PTR = OFF_EPI_BAR + 8;
   static constexpr uint32_t OFF_ABORT = OFF_TMEM_PTR + 4;
   static constexpr uint32_t SMEM_BYTES = OFF_ABORT + 4 + 1024;   // + slack for the manual alignment
   static_assert(BN == 128 || BN == 256, "BN");
@@ -101,7 +103,7 @@ TBIK_DEVICE void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
 template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
   using C_ = Cfg<BN, STAGES, SLEVELS, PAIR>;
   constexpr uint32_t STAGE_BYTES = C_::STAGE_BYTES;
   constexpr int TILE_M = C_::TILE_M;
@@ -139,6 +141,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), PAIR ? 2 * NUM_EPI_WARPS : NUM_EPI_WARPS);  // pair: both CTAs' warps, on the leader's
     }
+    mbar_init(smem_base + C_::OFF_EPI_BAR, NUM_EPI_WARPS);
     fence_mbar_init();
   }
   if (warp == 0 && lane == 0) {
@@ -298,14 +301,19 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
         for (int w = 0; w < NW / 32; ++w) tmem_ld32(col + w * 32, *reinterpret_cast<uint32_t(*)[32]>(&t[w * 32]));
         tmem_wait_ld();
-      } else if (idx < C_::TMEM_LEVELS + SLEVELS) {
-        const uint32_t* sp = smem_stack + (idx - C_::TMEM_LEVELS) * C_::LEVEL_WORDS + epi_tid;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) t[w] = sp[w * EPI_THREADS];
       } else {
-        const uint32_t* gp = gl_stack + (idx - C_::TMEM_LEVELS - SLEVELS) * C_::LEVEL_WORDS + epi_tid;
+        // shared memory or scratch: 16 bytes per thread per access, a warp touches 512 contiguous bytes
+        const uint4* src = idx < C_::TMEM_LEVELS + SLEVELS
+            ? reinterpret_cast<const uint4*>(smem_stack + (idx - C_::TMEM_LEVELS) * C_::LEVEL_WORDS)
+            : reinterpret_cast<const uint4*>(gl_stack + (idx - C_::TMEM_LEVELS - SLEVELS) * C_::LEVEL_WORDS);
 #pragma unroll
-        for (int w = 0; w < NW; ++w) t[w] = gp[w * EPI_THREADS];
+        for (int w = 0; w < NW / 4; ++w) {
+          const uint4 q4 = src[w * EPI_THREADS + epi_tid];
+          t[4 * w] = q4.x;
+          t[4 * w + 1] = q4.y;
+          t[4 * w + 2] = q4.z;
+          t[4 * w + 3] = q4.w;
+        }
       }
     };
     auto stack_store = [&](int lvl, const uint32_t (&v)[NW]) {
@@ -314,20 +322,44 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const uint32_t col = tmem_base + lane_off + C_::TMEM_STACK_COL0 + idx * (BN / 2) + h * (BN / 4);
 #pragma unroll
         for (int w = 0; w < NW / 32; ++w) tmem_st32(col + w * 32, *reinterpret_cast<const uint32_t(*)[32]>(&v[w * 32]));
-      } else if (idx < C_::TMEM_LEVELS + SLEVELS) {
-        uint32_t* sp = smem_stack + (idx - C_::TMEM_LEVELS) * C_::LEVEL_WORDS + epi_tid;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) sp[w * EPI_THREADS] = v[w];
       } else {
-        uint32_t* gp = gl_stack + (idx - C_::TMEM_LEVELS - SLEVELS) * C_::LEVEL_WORDS + epi_tid;
+        uint4* dst = idx < C_::TMEM_LEVELS + SLEVELS
+            ? reinterpret_cast<uint4*>(smem_stack + (idx - C_::TMEM_LEVELS) * C_::LEVEL_WORDS)
+            : reinterpret_cast<uint4*>(gl_stack + (idx - C_::TMEM_LEVELS - SLEVELS) * C_::LEVEL_WORDS);
 #pragma unroll
-        for (int w = 0; w < NW; ++w) gp[w * EPI_THREADS] = v[w];
+        for (int w = 0; w < NW / 4; ++w)
+          dst[w * EPI_THREADS + epi_tid] = make_uint4(v[4 * w], v[4 * w + 1], v[4 * w + 2], v[4 * w + 3]);
+      }
+    };
+
+    // C leaves through the TMA unit when possible: the finished tile is staged (128-byte swizzle) in the
+    // shared-memory slot of stack level 1, which is free once the tree is complete, and one thread issues
+    // one tiled store per 64 columns.  The slot may only be rewritten after those stores have read it.
+    const bool tma_c = SLEVELS > 0 && p.tma_store != 0;
+    bool staging_busy = false;
+    bool ok = true;
+    uint32_t epi_phase = 0;
+    // Rendezvous of the eight epilogue warps on an mbarrier with a bounded wait (a plain bar.sync would
+    // wait forever for a warp that has left after an abort).
+    auto epi_sync = [&]() {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_base + C_::OFF_EPI_BAR);
+      if (!mbar_wait_bounded(smem_base + C_::OFF_EPI_BAR, epi_phase, abort_flag, WAIT_LIMIT_NS)) {
+        ok = false;
+        role_failed = 6;
+      }
+      epi_phase ^= 1u;
+    };
+    auto staging_release = [&]() {
+      if (staging_busy) {
+        if (epi_tid == 0) bulk_wait_read_all();
+        epi_sync();
+        staging_busy = false;
       }
     };
 
     uint32_t s0[NW];  // the open level-0 group; once it closes, the node that climbs the tree
     uint32_t leaf_ctr = 0;
-    bool ok = true;
     for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
       int tm, tn;
       tile_coords(p, tile, tm, tn);
@@ -335,7 +367,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       T* crow = reinterpret_cast<T*>(p.C) + static_cast<int64_t>(row) * p.ldc;
       int c0 = 0;       // leaves already summed into the open level-0 group
       uint32_t g = 0;   // finished level-0 groups of this tile
-      for (int leaf = 0; leaf < p.T; ++leaf, ++leaf_ctr) {
+      for (int leaf = 0; ok && leaf < p.T; ++leaf, ++leaf_ctr) {
         const uint32_t a = leaf_ctr & 1u;
         const uint32_t aphase = (leaf_ctr >> 1) & 1u;
         if (!mbar_wait_bounded(tfull_bar(a), aphase, abort_flag, WAIT_LIMIT_NS)) {
@@ -382,7 +414,33 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           ++lvl;
         }
         if (lvl < p.L) {
+          if (lvl - 1 == C_::TMEM_LEVELS) staging_release();  // about to overwrite the staging slot
           stack_store(lvl, s0);
+        } else if (tma_c) {
+          staging_release();
+          // the slot is laid out per thread as a stack level but per row as a staged tile: nobody may
+          // write tile rows into it before every warp has popped its own level-1 words
+          epi_sync();
+          constexpr int CCH = C_::COLS_PER_WARP / 64;  // 64-column boxes per warp
+          const int r = q * 32 + lane;
+#pragma unroll
+          for (int cc = 0; cc < CCH; ++cc) {
+            uint8_t* box = reinterpret_cast<uint8_t*>(smem_stack) + (h * CCH + cc) * (BM * 128) + r * 128;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              *reinterpret_cast<uint4*>(box + ((u ^ (r & 7)) << 4)) =
+                  make_uint4(s0[cc * 32 + 4 * u], s0[cc * 32 + 4 * u + 1], s0[cc * 32 + 4 * u + 2], s0[cc * 32 + 4 * u + 3]);
+          }
+          fence_proxy_async_smem();
+          epi_sync();
+          if (ok && epi_tid == 0) {
+            const uint32_t sbase = smem_base + C_::OFF_STACK;
+            const int row0 = tm * TILE_M + static_cast<int>(cta_rank) * BM;
+#pragma unroll
+            for (int b = 0; b < BN / 64; ++b) tma_store_2d(&tmap_c, sbase + b * (BM * 128), tn * BN + b * 64, row0);
+            bulk_commit_group();
+          }
+          staging_busy = true;
         } else if (row < p.M) {
           // root of the tile's tree: write this thread's BN/2 columns of C
 #pragma unroll
@@ -409,6 +467,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 
   // ---------------------------------------------------------------- tear-down
+  if (warp == EPI_WARP0 && lane == 0) bulk_wait_read_all();  // staged C tiles have left shared memory
   tc_fence_before_sync();
   __syncwarp();
   if constexpr (PAIR) cluster_sync_all(); else __syncthreads();
@@ -449,7 +508,8 @@ EncodeTiledFn get_encode_fn() {
 }
 
 // Row-major [rows, K] 16-bit matrix, row stride `ld` elements, box = 64 (K) x `box_rows` rows.
-int make_tmap(CUtensorMap* tm, int dtype, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows) {
+int make_tmap(CUtensorMap* tm, int dtype, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows,
+              bool quiet = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return set_error(TBIK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
@@ -460,6 +520,7 @@ int make_tmap(CUtensorMap* tm, int dtype, const void* base, int64_t rows, int64_
   CUresult r = fn(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
+    if (quiet) return TBIK_ERR_CUDA;
     char msg[160];
     snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld K=%lld ld=%lld)", (int)r,
              (long long)rows, (long long)K, (long long)ld);
@@ -471,7 +532,8 @@ int make_tmap(CUtensorMap* tm, int dtype, const void* base, int64_t rows, int64_
 __device__ uint32_t g_gemm_status[4];
 
 template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
+           cudaStream_t stream) {
   using C_ = Cfg<BN, STAGES, SLEVELS, PAIR>;
   static bool configured[64] = {};
   int dev = 0;
@@ -496,10 +558,10 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, in
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, p);
     if (e != cudaSuccess) return set_cuda_error(e, "tree_gemm_kernel launch");
   } else {
-    kernel<<<grid, NUM_THREADS, C_::SMEM_BYTES, stream>>>(ta, tb, p);
+    kernel<<<grid, NUM_THREADS, C_::SMEM_BYTES, stream>>>(ta, tb, tc, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return set_cuda_error(e, "tree_gemm_kernel launch");
   }
@@ -529,13 +591,13 @@ constexpr Variant kVariants[4][2] = {
 };
 
 template <typename T>
-int launch_variant(int tiling, bool deep, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
-                   cudaStream_t stream) {
+int launch_variant(int tiling, bool deep, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                   const GemmParams& p, int grid, cudaStream_t stream) {
   switch (tiling) {
-    case 1: return deep ? launch<T, 128, 4, 2, false>(ta, tb, p, grid, stream) : launch<T, 128, 6, 0, false>(ta, tb, p, grid, stream);
-    case 2: return deep ? launch<T, 128, 5, 2, true>(ta, tb, p, grid, stream) : launch<T, 128, 8, 0, true>(ta, tb, p, grid, stream);
-    case 3: return launch<T, 256, 3, 1, false>(ta, tb, p, grid, stream);
-    case 4: return launch<T, 256, 5, 1, true>(ta, tb, p, grid, stream);
+    case 1: return deep ? launch<T, 128, 4, 2, false>(ta, tb, tc, p, grid, stream) : launch<T, 128, 6, 0, false>(ta, tb, tc, p, grid, stream);
+    case 2: return deep ? launch<T, 128, 5, 2, true>(ta, tb, tc, p, grid, stream) : launch<T, 128, 8, 0, true>(ta, tb, tc, p, grid, stream);
+    case 3: return launch<T, 256, 3, 1, false>(ta, tb, tc, p, grid, stream);
+    case 4: return launch<T, 256, 5, 1, true>(ta, tb, tc, p, grid, stream);
     default: return set_error(TBIK_ERR_ARG, "unknown tiling");
   }
 }
@@ -671,15 +733,23 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
   p.L = L;
   p.tiles_m = pl.tiles_m;
   p.tiles_n = pl.tiles_n;
-  p.group_m = v.pair ? 4 : 8;
+  p.group_m = v.pair ? 8 : 16;  // 2048 rows of A per group: a wave of CTAs covers a near-square block of C
   p.scratch = static_cast<uint32_t*>(workspace);
   p.scratch_levels = pl.scratch_levels;
   void* status_ptr = nullptr;
   cudaGetSymbolAddress(&status_ptr, g_gemm_status);
   p.status = static_cast<uint32_t*>(status_ptr);
 
-  if (dtype == TBIK_DTYPE_BF16) return launch_variant<__nv_bfloat16>(pl.tiling, pl.deep, ta, tb, p, pl.grid, stream);
-  return launch_variant<__half>(pl.tiling, pl.deep, ta, tb, p, pl.grid, stream);
+  // C through TMA stores when its layout allows a tensor map (64-column boxes of 128 rows); otherwise the
+  // epilogue threads store their rows directly.
+  CUtensorMap tc{};
+  p.tma_store = 0;
+  if ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && ldc % 8 == 0 &&
+      make_tmap(&tc, dtype, C, M, N, ldc, BM, true) == TBIK_OK)
+    p.tma_store = 1;
+
+  if (dtype == TBIK_DTYPE_BF16) return launch_variant<__nv_bfloat16>(pl.tiling, pl.deep, ta, tb, tc, p, pl.grid, stream);
+  return launch_variant<__half>(pl.tiling, pl.deep, ta, tb, tc, p, pl.grid, stream);
 }
 
 // ---------------------------------------------------------------- the entry point that allocates nothing

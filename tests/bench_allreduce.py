@@ -1,0 +1,86 @@
+"""Tree all-reduce alone (BASELINE config 3): latency and bandwidth of the peer-to-peer tree kernels
+against NCCL all_reduce and the all_gather + ordered-adds path, bf16, 8 KB ... 64 MB, one process per GPU.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        tests/bench_allreduce.py [--iters 20] [--warmup 5] [--max-mb 64]
+
+Counterpart of the reference's tests/bench_allreduce.py:19-135, with device timing (CUDA events, max
+over ranks) instead of wall clock and without the clone inside the timed region.
+Rank 0 prints one JSON line per size.
+"""
+import argparse
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--max-mb", type=int, default=64)
+    args = ap.parse_args()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from llm_reproducibility_b200.mini_allreduce import CustomTreeAllreduce
+    from llm_reproducibility_b200.tbik.tree_based_all_reduce import tree_all_reduce_sum_native
+
+    max_bytes = args.max_mb << 20
+    ar = CustomTreeAllreduce(group=dist.group.WORLD, device=dev, max_size=max_bytes + (1 << 20))
+    assert not ar.disabled
+
+    def timed(fn):
+        for _ in range(args.warmup):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / args.iters], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) * 1e3  # us
+
+    nbytes = 8192
+    while nbytes <= max_bytes:
+        numel = nbytes // 2
+        g = torch.Generator(device=dev).manual_seed(1000 + rank)
+        x = torch.randn(numel, generator=g, device=dev).to(torch.bfloat16)
+        out = torch.empty_like(x)
+        view = ar.registered_view((numel,), torch.bfloat16)
+        view.copy_(x)
+        nccl_buf = x.clone()
+        res = {
+            "bytes": nbytes, "world": world,
+            "tree_p2p_staged_us": timed(lambda: ar.all_reduce(x, out=out)),
+            "tree_p2p_registered_us": timed(lambda: ar.all_reduce(view, out=out, registered=True)),
+            "nccl_allreduce_us": timed(lambda: dist.all_reduce(nccl_buf)),
+            "allgather_adds_us": timed(lambda: tree_all_reduce_sum_native(x, None)),
+        }
+        t = res["tree_p2p_registered_us"] * 1e-6
+        res["algbw_GBs"] = nbytes / t / 1e9
+        res["busbw_GBs"] = nbytes * 2 * (world - 1) / world / t / 1e9
+        ar.check_status()
+        if rank == 0:
+            print(json.dumps(res), flush=True)
+        nbytes *= 2
+    dist.barrier()
+    ar.close()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
