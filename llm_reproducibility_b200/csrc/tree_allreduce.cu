@@ -230,8 +230,17 @@ allreduce_oneshot_kernel(const RankData* dp_ptr, RankSignals sg, Signal* self, v
   if (!block_barrier<NG>(sg, self, rank, status, limit_ns, 1, &fail)) return;
   uint4* o = reinterpret_cast<uint4*>(out);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < npacks; idx += stride)
-    o[idx] = reduce_pack<T, NG, TREE>(dp, idx);
+  int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // kUnroll independent packs per thread keep kUnroll * NG 16-byte peer loads in flight
+  constexpr int kUnroll = NG >= 8 ? 2 : 4;
+  for (; idx + (kUnroll - 1) * stride < npacks; idx += kUnroll * stride) {
+    uint4 r[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) r[u] = reduce_pack<T, NG, TREE>(dp, idx + u * stride);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) o[idx + u * stride] = r[u];
+  }
+  for (; idx < npacks; idx += stride) o[idx] = reduce_pack<T, NG, TREE>(dp, idx);
   // peers may still be reading this rank's buffer: nobody leaves before everybody is done
   block_barrier<NG>(sg, self, rank, status, limit_ns, 3, &fail);
 }
@@ -254,7 +263,18 @@ allreduce_twoshot_kernel(const RankData* dp_ptr, RankSignals sg, Signal* self, v
 
   if (!block_barrier<NG>(sg, self, rank, status, limit_ns, 1, &fail)) return;
   // reduce-scatter: this rank owns packs [start, end)
-  for (int64_t idx = start + tid; idx < end; idx += stride) scratch[rank][idx - start] = reduce_pack<T, NG, TREE>(dp, idx);
+  {
+    constexpr int kUnroll = NG >= 8 ? 2 : 4;
+    int64_t idx = start + tid;
+    for (; idx + (kUnroll - 1) * stride < end; idx += kUnroll * stride) {
+      uint4 r[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) r[u] = reduce_pack<T, NG, TREE>(dp, idx + u * stride);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) scratch[rank][idx + u * stride - start] = r[u];
+    }
+    for (; idx < end; idx += stride) scratch[rank][idx - start] = reduce_pack<T, NG, TREE>(dp, idx);
+  }
   // release this rank's scratch writes / acquire the peers'
   if (!block_barrier<NG>(sg, self, rank, status, limit_ns, 2, &fail)) return;
   // all-gather: same thread <-> same pack offset in both phases
@@ -379,12 +399,13 @@ int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, vo
 
   const int64_t npacks = static_cast<int64_t>(bytes / 16);
   size_t one_max = c->oneshot_max_bytes;
-  if (one_max == 0) one_max = c->world <= 2 ? (1u << 20) : (c->world <= 4 ? (512u << 10) : (256u << 10));
+  // two ranks: both schedules pull the same number of remote bytes, one-shot skips the scratch round trip
+  if (one_max == 0) one_max = c->world <= 2 ? ~size_t(0) : (c->world <= 4 ? (512u << 10) : (256u << 10));
   bool twoshot = c->world > 1 && bytes > one_max && c->full_nvlink;
   if (twoshot) {
     const int64_t part = npacks / c->world + npacks % c->world;
     if (static_cast<size_t>(part) * 16 > c->scratch_bytes) {
-      if (bytes <= (8u << 20)) twoshot = false;  // fits the one-shot schedule comfortably
+      if (bytes <= (8u << 20)) twoshot = false;  // small enough for the one-shot schedule
       else return set_error(TBIK_ERR_SHAPE, "all-reduce: message needs more scratch than the meta buffer provides (raise max_size)");
     }
   }
