@@ -80,7 +80,7 @@ int tbik_gemm_ws(const void* A, const void* W, void* C, int M, int N, int K, int
 
 /* As tbik_gemm_ws, with the schedule exposed: at most `max_ctas` CTAs (0 = one per SM) and
  * `tiling` 0 = automatic, 1 = 128x128 tile per CTA, 2 = 256x128 per CTA pair, 3 = 128x256 per CTA,
- * 4 = 256x256 per CTA pair.  The result does not depend on either; the entry point exists so that
+ * 4 = 256x256 per CTA pair, 5 = 128x64 per CTA, 6 = 128x32 per CTA.  The result does not depend on either; the entry point exists so that
  * tests can prove that. */
 int tbik_gemm_ex(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
                  int dtype, int leaf, int node_dtype, int max_ctas, int tiling, void* workspace,

@@ -22,7 +22,9 @@
 //
 // Tilings (template parameters BN, PAIR); all give identical bits, asserted by the tests:
 //   BN=128 single   128x128 tile, UMMA 128x128x16; 256 TMEM columns left for 4 stack levels; no scratch.
-//                   Used for small M (more tiles) and when no scratch buffer is supplied.
+//                   Used when there are too few rows for 128x256 tiles to occupy the SMs, or no scratch.
+//   BN=64 / BN=32   128x64 and 128x32 tiles for small M (decode): the GEMM then streams W from HBM and
+//                   needs every SM pulling; the whole stack fits TMEM.
 //   BN=256 single   128x256 tile, UMMA 128x256x16: the instruction shape that runs the tensor core at
 //                   full rate and needs 25% less shared-memory traffic per FLOP; the accumulators
 //                   fill TMEM, so the stack above level 0 lives in shared memory and scratch.
@@ -71,7 +73,8 @@ struct Cfg {
   static constexpr uint32_t B_STAGE_BYTES = B_ROWS * BK * 2;
   static constexpr uint32_t STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int TILE_M = PAIR ? 2 * BM : BM;              // rows of C per scheduled tile
-  static constexpr int COLS_PER_WARP = BN / 2;                   // two warps share a TMEM lane quadrant
+  static constexpr int EPI_HALVES = BN >= 64 ? 2 : 1;            // warps per TMEM lane quadrant that drain columns
+  static constexpr int COLS_PER_WARP = BN / EPI_HALVES;
   static constexpr int NCH = COLS_PER_WARP / CHUNK;              // chunks per thread per leaf
   static constexpr int LEVEL_WORDS = EPI_THREADS * NCH * (CHUNK / 2);  // packed words of one stack level
   static constexpr int TMEM_LEVELS = (static_cast<int>(TMEM_COLS) - 2 * BN) / (BN / 2);
@@ -86,7 +89,7 @@ struct Cfg {
   static constexpr uint32_t OFF_TMEM_PTR = OFF_EPI_BAR + 8;
   static constexpr uint32_t OFF_ABORT = OFF_TMEM_PTR + 4;
   static constexpr uint32_t SMEM_BYTES = OFF_ABORT + 4 + 1024;   // + slack for the manual alignment
-  static_assert(BN == 128 || BN == 256, "BN");
+  static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "BN");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
@@ -297,9 +300,13 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     auto stack_load = [&](int lvl, uint32_t (&t)[NW]) {
       const int idx = lvl - 1;
       if (idx < C_::TMEM_LEVELS) {
-        const uint32_t col = tmem_base + lane_off + C_::TMEM_STACK_COL0 + idx * (BN / 2) + h * (BN / 4);
+        const uint32_t col = tmem_base + lane_off + C_::TMEM_STACK_COL0 + idx * (BN / 2) + h * (C_::COLS_PER_WARP / 2);
+        if constexpr (NW == 16) {
+          tmem_ld16(col, *reinterpret_cast<uint32_t(*)[16]>(&t[0]));
+        } else {
 #pragma unroll
-        for (int w = 0; w < NW / 32; ++w) tmem_ld32(col + w * 32, *reinterpret_cast<uint32_t(*)[32]>(&t[w * 32]));
+          for (int w = 0; w < NW / 32; ++w) tmem_ld32(col + w * 32, *reinterpret_cast<uint32_t(*)[32]>(&t[w * 32]));
+        }
         tmem_wait_ld();
       } else {
         // shared memory or scratch: 16 bytes per thread per access, a warp touches 512 contiguous bytes
@@ -319,9 +326,13 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     auto stack_store = [&](int lvl, const uint32_t (&v)[NW]) {
       const int idx = lvl - 1;
       if (idx < C_::TMEM_LEVELS) {
-        const uint32_t col = tmem_base + lane_off + C_::TMEM_STACK_COL0 + idx * (BN / 2) + h * (BN / 4);
+        const uint32_t col = tmem_base + lane_off + C_::TMEM_STACK_COL0 + idx * (BN / 2) + h * (C_::COLS_PER_WARP / 2);
+        if constexpr (NW == 16) {
+          tmem_st16(col, *reinterpret_cast<const uint32_t(*)[16]>(&v[0]));
+        } else {
 #pragma unroll
-        for (int w = 0; w < NW / 32; ++w) tmem_st32(col + w * 32, *reinterpret_cast<const uint32_t(*)[32]>(&v[w * 32]));
+          for (int w = 0; w < NW / 32; ++w) tmem_st32(col + w * 32, *reinterpret_cast<const uint32_t(*)[32]>(&v[w * 32]));
+        }
       } else {
         uint4* dst = idx < C_::TMEM_LEVELS + SLEVELS
             ? reinterpret_cast<uint4*>(smem_stack + (idx - C_::TMEM_LEVELS) * C_::LEVEL_WORDS)
@@ -358,6 +369,22 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     };
 
+    if (h >= C_::EPI_HALVES) {
+      // narrow tiles: this warp has no columns to drain; it only keeps the accumulator hand-shake going
+      uint32_t ctr = 0;
+      for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
+        for (int leaf = 0; ok && leaf < p.T; ++leaf, ++ctr) {
+          const uint32_t a = ctr & 1u;
+          if (!mbar_wait_bounded(tfull_bar(a), (ctr >> 1) & 1u, abort_flag, WAIT_LIMIT_NS)) {
+            ok = false;
+            role_failed = 4;
+            break;
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * a);
+        }
+      }
+    } else {
     uint32_t s0[NW];  // the open level-0 group; once it closes, the node that climbs the tree
     uint32_t leaf_ctr = 0;
     for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
@@ -464,6 +491,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
     }
+    }  // draining warps
   }
 
   // ---------------------------------------------------------------- tear-down
@@ -583,11 +611,13 @@ constexpr Variant variant_of() {
 }
 
 // tiling code -> (shallow, deep) variants; the deep one trades pipeline stages for stack levels
-constexpr Variant kVariants[4][2] = {
+constexpr Variant kVariants[6][2] = {
     {variant_of<128, 6, 0, false>(), variant_of<128, 4, 2, false>()},
     {variant_of<128, 8, 0, true>(), variant_of<128, 5, 2, true>()},
     {variant_of<256, 3, 1, false>(), variant_of<256, 3, 1, false>()},
     {variant_of<256, 5, 1, true>(), variant_of<256, 5, 1, true>()},
+    {variant_of<64, 8, 0, false>(), variant_of<64, 8, 0, false>()},
+    {variant_of<32, 8, 0, false>(), variant_of<32, 8, 0, false>()},
 };
 
 template <typename T>
@@ -598,6 +628,8 @@ int launch_variant(int tiling, bool deep, const CUtensorMap& ta, const CUtensorM
     case 2: return deep ? launch<T, 128, 5, 2, true>(ta, tb, tc, p, grid, stream) : launch<T, 128, 8, 0, true>(ta, tb, tc, p, grid, stream);
     case 3: return launch<T, 256, 3, 1, false>(ta, tb, tc, p, grid, stream);
     case 4: return launch<T, 256, 5, 1, true>(ta, tb, tc, p, grid, stream);
+    case 5: return launch<T, 64, 8, 0, false>(ta, tb, tc, p, grid, stream);
+    case 6: return launch<T, 32, 8, 0, false>(ta, tb, tc, p, grid, stream);
     default: return set_error(TBIK_ERR_ARG, "unknown tiling");
   }
 }
@@ -663,23 +695,33 @@ static Plan make_plan(int tiling, int M, int N, int L, int max_ctas) {
   return pl;
 }
 
-// Automatic choice: one 128x128 tile per CTA while M fits a single row block (more tiles, no scratch);
-// 128x256 tiles beyond that, if the caller's scratch buffer is large enough for the tree's upper levels.
+// Automatic choice: the widest tile that still gives (nearly) every SM a tile -- wide tiles run the tensor
+// pipe faster, but with few rows of C the GEMM streams W from HBM and needs all SMs pulling.  128x256 needs
+// the caller's scratch for the upper tree levels; without it the 128-wide and narrower tilings are used.
 static Plan auto_plan(int M, int N, int L, int max_ctas, size_t ws_bytes, bool have_ws) {
-  if (M > BM) {
-    Plan wide = make_plan(3, M, N, L, max_ctas);
-    if (wide.scratch_bytes == 0 || (have_ws && wide.scratch_bytes <= ws_bytes)) return wide;
+  int ctas = sm_count();
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  const int enough = ctas - ctas / 5;
+  const int order[4] = {3, 1, 5, 6};
+  Plan best{};
+  bool have = false;
+  for (int i = 0; i < 4; ++i) {
+    Plan pl = make_plan(order[i], M, N, L, max_ctas);
+    if (pl.scratch_bytes > 0 && !(have_ws && pl.scratch_bytes <= ws_bytes)) continue;
+    if (pl.tiles_m * pl.tiles_n >= enough) return pl;
+    if (!have || pl.tiles_m * pl.tiles_n > best.tiles_m * best.tiles_n) {
+      best = pl;
+      have = true;
+    }
   }
-  return make_plan(1, M, N, L, max_ctas);
+  return have ? best : make_plan(1, M, N, L, max_ctas);
 }
 
 size_t gemm_workspace_bytes(int M, int N, int64_t K, int leaf) {
   int T, F, L;
   if (M <= 0 || N <= 0 || tree_shape(K, leaf, &T, &F, &L) != TBIK_OK) return 0;
-  size_t need = 0;
-  if (M > BM) need = make_plan(3, M, N, L, 0).scratch_bytes;
-  const size_t narrow = make_plan(1, M, N, L, 0).scratch_bytes;
-  return need > narrow ? need : narrow;
+  // what the automatic choice would like to have if scratch were unlimited
+  return auto_plan(M, N, L, 0, ~size_t(0), true).scratch_bytes;
 }
 
 int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
@@ -691,7 +733,7 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
     return set_error(TBIK_ERR_DTYPE, "tbik_gemm: only node_dtype = TBIK_NODE_INPUT is implemented");
   if (M < 0 || N < 0 || K <= 0) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: M, N must be >= 0 and K > 0");
   if (leaf <= 0 || leaf % BK != 0) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: leaf must be a positive multiple of 64");
-  if (tiling < 0 || tiling > 4) return set_error(TBIK_ERR_ARG, "tbik_gemm: tiling must be 0..4");
+  if (tiling < 0 || tiling > 6) return set_error(TBIK_ERR_ARG, "tbik_gemm: tiling must be 0..6");
   int T, F, L;
   if (tree_shape(K, leaf, &T, &F, &L) != TBIK_OK)
     return set_error(TBIK_ERR_SHAPE, "tbik_gemm: K must be a multiple of the leaf width");

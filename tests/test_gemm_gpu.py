@@ -81,17 +81,23 @@ def test_deep_trees_use_the_shared_memory_levels(mm, K):
     assert torch.equal(bits(C.cpu()), bits(tbik_matmul_ref(A, B)))
 
 
-def test_very_deep_tree_needs_scratch():
-    """L = 8 (K = 65536): more levels than fit on chip.  Without scratch the call is refused with a
-    message naming the need; with scratch it runs (levels above the on-chip ones live in L2)."""
+def test_very_deep_tree_scratch_rules():
+    """L = 8 (K = 65536).  The 256-wide tilings keep only one level above the registers on chip and need
+    scratch for the rest: without it they are refused with a message naming the need.  The entry point
+    without scratch still works (it picks a tiling whose whole stack fits tensor memory)."""
     from llm_reproducibility_b200 import _lib
     A, B = exact_int_inputs(130, 65536, 136, torch.bfloat16, seed=8, amax=3)
     Ad, W = A.cuda(), B.cuda().t().contiguous()
+    ref = tbik_matmul_ref(A, B)
     C = torch.empty(130, 136, dtype=torch.bfloat16, device="cuda")
     s = torch.cuda.current_stream().cuda_stream
-    rc = _lib.lib().tbik_gemm(Ad.data_ptr(), W.data_ptr(), C.data_ptr(), 130, 136, 65536, 65536, 65536, 136, 0, 256, 0, s)
+    L = _lib.lib()
+    assert L.tbik_gemm(Ad.data_ptr(), W.data_ptr(), C.data_ptr(), 130, 136, 65536, 65536, 65536, 136, 0, 256, 0, s) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(bits(C.cpu()), bits(ref))
+    rc = L.tbik_gemm_ex(Ad.data_ptr(), W.data_ptr(), C.data_ptr(), 130, 136, 65536, 65536, 65536, 136, 0, 256, 0,
+                        0, 3, None, 0, s)
     assert rc == -2 and "scratch" in _lib.last_error()
-    ref = tbik_matmul_ref(A, B)
     for tiling in TILINGS:
         assert torch.equal(bits(_gemm_ex(Ad, W, 130, 136, 65536, 0, tiling).cpu()), bits(ref)), tiling
 
@@ -101,8 +107,8 @@ def test_entry_point_without_scratch_matches_the_one_with_scratch():
     from llm_reproducibility_b200 import _lib
     from llm_reproducibility_b200.tbik.tree_based_matmul import matmul_tp_persistent
     L = _lib.lib()
-    M, K, N = 1000, 12288, 1024
-    assert L.tbik_gemm_workspace_bytes(M, N, K, 256) > 0          # (3,5) tree: two levels go to scratch
+    M, K, N = 1000, 12288, 4096
+    assert L.tbik_gemm_workspace_bytes(M, N, K, 256) > 0          # 128x256 tiles, 5-level tree: 3 levels go to scratch
     assert L.tbik_gemm_workspace_bytes(64, N, K, 256) == 0        # small M: no scratch needed
     g = torch.Generator(device="cuda").manual_seed(1)
     A = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
@@ -199,7 +205,7 @@ def _gemm_ex(Ad, W, M, N, K, ctas, tiling, dtype_code=0, leaf=256, workspace=Tru
     return C
 
 
-TILINGS = [1, 2, 3, 4]
+TILINGS = [1, 2, 3, 4, 5, 6]
 
 
 @pytest.mark.parametrize("tiling", TILINGS)
