@@ -173,6 +173,25 @@ int tbik_ar_register_graph_buffers(tbik_ar_t comm, const void* const* handles, c
  * value seen, barrier id.  No counterpart in the reference (custom_all_reduce.cuh:182,186 spin forever). */
 int tbik_ar_status(tbik_ar_t comm, uint32_t out[8]);
 
+/* The whole row-split layer in ONE kernel launch: out = tree-all-reduce over ranks of (A * W^T), with the
+ * K reduction of every rank in the fixed tree order and the cross-rank levels in the rank-pair order --
+ * bitwise what tbik_gemm_ws followed by tbik_ar_tree_allreduce gives.  The last `comm_ctas` CTAs of the
+ * grid (0 = built-in choice) do no multiplication: as soon as every rank has published an output tile they
+ * pull the partial tiles over NVLink (plain peer loads), reduce the tiles this rank owns, and copy the
+ * others from their owners, while the remaining CTAs keep computing later tiles.  `reg_buffer` is a
+ * registered buffer of at least M*N*2 bytes that receives this rank's partial result (the GEMM writes it
+ * directly; there is no staging copy); `workspace` as for tbik_gemm_ws
+ * (tbik_ar_gemm_workspace_bytes).  N and ldo must be multiples of 8; 2, 4 or 8 ranks; not capturable.
+ * Collective: every rank calls it in the same order with the same sizes.
+ * Replaces: the sequence matmul_tp_persistent -> tree_all_reduce_sum in the patched forward,
+ *           src/patch/patch_tp_invariant.py:31-34 (and the staging copy at custom_all_reduce.cu:112-114). */
+int tbik_ar_gemm_tree_allreduce(tbik_ar_t comm, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
+                                int64_t ldw, int64_t ldo, int dtype, int leaf, void* reg_buffer, size_t reg_buffer_bytes,
+                                void* workspace, size_t workspace_bytes, int comm_ctas, tbik_stream_t stream);
+
+/* Scratch bytes tbik_ar_gemm_tree_allreduce wants for these sizes (0 if none).  No counterpart in the reference. */
+size_t tbik_ar_gemm_workspace_bytes(int M, int N, int64_t K, int leaf);
+
 #ifdef __cplusplus
 }
 #endif

@@ -14,7 +14,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libtbik_b200.so")
 
 SOURCES = ["capi.cu", "tree_gemm_sm100a.cu", "tree_allreduce.cu"]
-HEADERS = ["ptx_sm100a.cuh", "tbik_internal.h", os.path.join("..", "..", "include", "tbik.h")]
+HEADERS = ["ptx_sm100a.cuh", "ar_common.cuh", "tbik_internal.h", os.path.join("..", "..", "include", "tbik.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -105,4 +105,13 @@ int tbik_ar_register_graph_buffers(tbik_ar_t comm, const void* const* handles, c
 
 int tbik_ar_status(tbik_ar_t comm, uint32_t out[8]) { return tbik::ar_status(comm, out); }
 
+size_t tbik_ar_gemm_workspace_bytes(int M, int N, int64_t K, int leaf) { return tbik::gemm_fused_workspace_bytes(M, N, K, leaf); }
+
+int tbik_ar_gemm_tree_allreduce(tbik_ar_t comm, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
+                                int64_t ldw, int64_t ldo, int dtype, int leaf, void* reg_buffer, size_t reg_buffer_bytes,
+                                void* workspace, size_t workspace_bytes, int comm_ctas, tbik_stream_t stream) {
+  return tbik::ar_gemm_tree_allreduce(comm, A, W, out, M, N, K, lda, ldw, ldo, dtype, leaf, reg_buffer, reg_buffer_bytes,
+                                      workspace, workspace_bytes, comm_ctas, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -123,6 +123,8 @@ TBIK_DEVICE void tma_store_2d(const void* tmap, uint32_t smem_src, int32_t x, in
 TBIK_DEVICE void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // All bulk stores committed by this thread have finished READING shared memory.
 TBIK_DEVICE void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// All bulk stores committed by this thread are complete (their global writes performed).
+TBIK_DEVICE void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // Named barrier over `count` threads (a multiple of 32), separate from __syncthreads' barrier 0.
 TBIK_DEVICE void named_barrier_sync(uint32_t id, uint32_t count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");

@@ -30,169 +30,13 @@
 #include <unordered_map>
 #include <vector>
 
+#include "ar_common.cuh"
 #include "tbik_internal.h"
 
 namespace tbik {
 
-constexpr int kMaxRanks = 8;
-constexpr int kMaxBlocks = 160;
 constexpr int kThreads = 512;
 constexpr uint64_t kArWaitLimitNs = 2000000000ull;  // default bound of one barrier wait
-
-struct alignas(128) Signal {
-  uint32_t epoch[kMaxBlocks][kMaxRanks];  // private to the owning rank: last epoch used by (block, thread)
-  uint32_t flag[kMaxBlocks][kMaxRanks];   // written by peers: flag[b][r] = last epoch announced by rank r, block b
-};
-
-struct alignas(16) RankData {
-  const void* ptrs[kMaxRanks];
-};
-
-struct RankSignals {
-  Signal* sig[kMaxRanks];
-};
-
-// status record (host-mapped): [0] code (0 ok, 1 barrier timeout) [1] rank [2] block [3] peer
-//                              [4] expected epoch [5] seen value [6] which barrier (1 start, 2 middle, 3 end)
-struct ArStatus {
-  uint32_t w[8];
-};
-
-__device__ __forceinline__ uint64_t ar_timer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ void st_flag_release(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_flag_acquire(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 ld_pack(const void* p) {
-  uint4 v;
-  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
-  return v;
-}
-
-// Per-block barrier across `NG` ranks.  Returns false (for every thread of the block) if a wait
-// ran out.  `which` only labels the status record.
-template <int NG>
-__device__ __forceinline__ bool block_barrier(const RankSignals& sg, Signal* self, int rank, ArStatus* status,
-                                              uint64_t limit_ns, int which, uint32_t* smem_fail) {
-  __syncthreads();  // all data accesses of the previous phase are done (and ordered before the release below)
-  if (threadIdx.x < NG) {
-    const int peer = threadIdx.x;
-    const uint32_t e = self->epoch[blockIdx.x][peer] + 1u;
-    self->epoch[blockIdx.x][peer] = e;
-    st_flag_release(&sg.sig[peer]->flag[blockIdx.x][rank], e);
-    const uint32_t* mine = &self->flag[blockIdx.x][peer];
-    uint32_t seen = ld_flag_acquire(mine);
-    if (static_cast<int32_t>(seen - e) < 0) {
-      const uint64_t t0 = ar_timer_ns();
-      uint32_t it = 0;
-      while (true) {
-        seen = ld_flag_acquire(mine);
-        if (static_cast<int32_t>(seen - e) >= 0) break;
-        if ((++it & 255u) == 0u && ar_timer_ns() - t0 > limit_ns) {
-          if (atomicCAS(&status->w[0], 0u, 1u) == 0u) {
-            status->w[1] = rank;
-            status->w[2] = blockIdx.x;
-            status->w[3] = peer;
-            status->w[4] = e;
-            status->w[5] = seen;
-            status->w[6] = which;
-            __threadfence_system();
-          }
-          *smem_fail = 1u;
-          break;
-        }
-      }
-    }
-  }
-  __syncthreads();
-  return *smem_fail == 0u;
-}
-
-template <typename T>
-struct Elem;
-template <>
-struct Elem<float> {
-  __device__ static uint4 add(uint4 a, uint4 b) {
-    uint4 r;
-    r.x = __float_as_uint(__uint_as_float(a.x) + __uint_as_float(b.x));
-    r.y = __float_as_uint(__uint_as_float(a.y) + __uint_as_float(b.y));
-    r.z = __float_as_uint(__uint_as_float(a.z) + __uint_as_float(b.z));
-    r.w = __float_as_uint(__uint_as_float(a.w) + __uint_as_float(b.w));
-    return r;
-  }
-  static constexpr int kPerPack = 4;
-  __device__ static void up(uint4 a, float (&f)[8]) {
-    f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
-    f[4] = f[5] = f[6] = f[7] = 0.f;
-  }
-  __device__ static uint4 down(const float (&f)[8]) {
-    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
-  }
-};
-template <>
-struct Elem<__half> {
-  __device__ static uint32_t add2(uint32_t a, uint32_t b) {
-    __half2 r = __hadd2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
-    return *reinterpret_cast<uint32_t*>(&r);
-  }
-  __device__ static uint4 add(uint4 a, uint4 b) { return make_uint4(add2(a.x, b.x), add2(a.y, b.y), add2(a.z, b.z), add2(a.w, b.w)); }
-  static constexpr int kPerPack = 8;
-  __device__ static void up(uint4 a, float (&f)[8]) {
-    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-      f[2 * i] = t.x;
-      f[2 * i + 1] = t.y;
-    }
-  }
-  __device__ static uint4 down(const float (&f)[8]) {
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      __half2 t = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
-      w[i] = *reinterpret_cast<uint32_t*>(&t);
-    }
-    return make_uint4(w[0], w[1], w[2], w[3]);
-  }
-};
-template <>
-struct Elem<__nv_bfloat16> {
-  __device__ static uint32_t add2(uint32_t a, uint32_t b) {
-    __nv_bfloat162 r = __hadd2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
-    return *reinterpret_cast<uint32_t*>(&r);
-  }
-  __device__ static uint4 add(uint4 a, uint4 b) { return make_uint4(add2(a.x, b.x), add2(a.y, b.y), add2(a.z, b.z), add2(a.w, b.w)); }
-  static constexpr int kPerPack = 8;
-  __device__ static void up(uint4 a, float (&f)[8]) {
-    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      f[2 * i] = __uint_as_float(w[i] << 16);
-      f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-    }
-  }
-  __device__ static uint4 down(const float (&f)[8]) {
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      __nv_bfloat162 t = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-      w[i] = *reinterpret_cast<uint32_t*>(&t);
-    }
-    return make_uint4(w[0], w[1], w[2], w[3]);
-  }
-};
 
 // One 16-byte pack reduced over the NG ranks.  TREE: rank-pair tree in T; else rank order in fp32.
 template <typename T, int NG, bool TREE>
@@ -312,6 +156,7 @@ struct Communicator {
   ArStatus* status_dev = nullptr;
   int sm_count = 0;
   bool poisoned = false;
+  uint32_t tile_epoch = 0;  // fused GEMM + all-reduce calls made so far (same on every rank)
 };
 
 static Communicator* as_comm(tbik_ar_t h) { return reinterpret_cast<Communicator*>(h); }
@@ -425,6 +270,40 @@ int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, vo
                 : dispatch_world<__half, false>(c, slot, out, npacks, twoshot, blocks, stream);
   return tree ? dispatch_world<__nv_bfloat16, true>(c, slot, out, npacks, twoshot, blocks, stream)
               : dispatch_world<__nv_bfloat16, false>(c, slot, out, npacks, twoshot, blocks, stream);
+}
+
+int ar_gemm_tree_allreduce(tbik_ar_t h, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
+                           int64_t ldw, int64_t ldo, int dtype, int leaf, void* reg_buffer, size_t reg_bytes,
+                           void* workspace, size_t ws_bytes, int comm_ctas, cudaStream_t stream) {
+  Communicator* c = as_comm(h);
+  if (!c) return set_error(TBIK_ERR_ARG, "fused GEMM + all-reduce: null communicator");
+  if (c->status_host && c->status_host->w[0] != 0) c->poisoned = true;
+  if (c->poisoned)
+    return set_error(TBIK_ERR_DEVICE, "all-reduce: an earlier call gave up waiting for a peer; the communicator must be rebuilt");
+  if (!reg_buffer) return set_error(TBIK_ERR_ARG, "fused GEMM + all-reduce needs a registered buffer for the partial results");
+  if (M > 0 && N > 0 && static_cast<size_t>(M) * N * 2 > reg_bytes)
+    return set_error(TBIK_ERR_SHAPE, "fused GEMM + all-reduce: partial result larger than the registered buffer");
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  cudaError_t e = cudaStreamIsCapturing(stream, &cap);
+  if (e != cudaSuccess) return set_cuda_error(e, "cudaStreamIsCapturing");
+  if (cap == cudaStreamCaptureStatusActive)
+    return set_error(TBIK_ERR_STATE, "fused GEMM + all-reduce cannot be captured (its call number is a kernel argument)");
+  auto it = c->registered.find(reg_buffer);
+  if (it == c->registered.end()) return set_error(TBIK_ERR_STATE, "fused GEMM + all-reduce: buffer is not registered!");
+  FusedArgs fa{};
+  fa.rank_data_slot = it->second;
+  for (int i = 0; i < c->world; ++i) fa.signals[i] = c->sg.sig[i];
+  fa.status_dev = c->status_dev;
+  fa.wait_limit_ns = c->wait_limit_ns;
+  fa.world = c->world;
+  fa.rank = c->rank;
+  fa.comm_ctas = comm_ctas > 0 ? comm_ctas : (c->world <= 2 ? 16 : (c->world <= 4 ? 24 : 32));
+  fa.epoch = c->tile_epoch + 1;
+  fa.out = out;
+  fa.ldo = ldo;
+  int rc = gemm_launch_fused(A, W, reg_buffer, M, N, K, lda, ldw, dtype, leaf, workspace, ws_bytes, fa, stream);
+  if (rc == TBIK_OK) ++c->tile_epoch;  // validation is identical on every rank, so the counters stay in step
+  return rc;
 }
 
 size_t ar_meta_size() { return sizeof(Signal); }

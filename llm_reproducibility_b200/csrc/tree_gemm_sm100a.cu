@@ -36,6 +36,7 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include "ar_common.cuh"
 #include "ptx_sm100a.cuh"
 #include "tbik_internal.h"
 
@@ -53,6 +54,19 @@ constexpr uint32_t TMEM_COLS = 512;
 constexpr int CHUNK = 32;  // accumulator columns drained per tcgen05.ld
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
 
+// Fused GEMM + tree all-reduce: the last `comm_ctas` CTAs of the grid do not compute; they reduce and gather
+// finished output tiles over peer memory while the other CTAs keep multiplying.
+struct FusedDev {
+  const RankData* rd;   // every rank's partial-result buffer ([M, N] row-major, IPC registered)
+  RankSignals sg;       // every rank's flag area
+  ArStatus* status;
+  uint64_t limit_ns;
+  int world, rank, comm_ctas;
+  uint32_t epoch;
+  void* out;            // this rank's final [M, N]
+  int64_t ldo;
+};
+
 struct GemmParams {
   void* C;
   int64_t ldc;
@@ -62,6 +76,7 @@ struct GemmParams {
   int tiles_m, tiles_n, group_m;  // tiles_m counts 128-row (single) or 256-row (pair) tiles
   uint32_t* scratch;     // global stack levels: [cta][level][chunk][word][epilogue thread]
   int scratch_levels;    // levels per CTA held in `scratch`
+  FusedDev f;            // used by the FUSED instantiation only
   int tma_store;         // 1: write C with TMA stores staged in the shared-memory stack slot (tmap_c valid)
   uint32_t* status;      // [0] error code, [1] block, [2] role, [3] SM cycles of block 0 (last launch)
 };
@@ -103,7 +118,88 @@ TBIK_DEVICE void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
   tn = local / gsz;
 }
 
-template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR>
+// ------------------------------------------------------------------ communication CTAs of the fused kernel
+// Tile t is owned by rank t mod n.  The owner waits until every rank has published its partial tile,
+// adds them in the rank-pair tree order ((0+1)+(2+3))+((4+5)+(6+7)) in the element type (the upper
+// levels of the same reduction tree the GEMM started), writes the sum over its own partial tile and
+// into its result, and publishes "done"; every other rank then copies the owner's tile into its own
+// result.  Tiles are visited in the order the GEMM CTAs produce them, so the NVLink traffic of a tile
+// overlaps the UMMAs of later tiles.  All waits are bounded; the final barrier keeps every rank's
+// buffers untouched until all ranks have finished reading.
+template <typename T, int NG, int BN>
+__device__ void comm_role_n(const GemmParams& p, int cidx) {
+  __shared__ uint32_t fail;
+  const FusedDev& f = p.f;
+  if (threadIdx.x == 0) fail = 0u;
+  __syncthreads();
+  const RankData rd = *f.rd;
+  Signal* self = f.sg.sig[f.rank];
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int64_t row_packs = p.N / 8;  // 16-byte packs per row of the partial buffers
+  const int64_t out_row_packs = f.ldo / 8;
+  uint4* out = reinterpret_cast<uint4*>(f.out);
+  uint4* mine = reinterpret_cast<uint4*>(const_cast<void*>(rd.ptrs[f.rank]));
+  const int tid = threadIdx.x;
+  for (int t = cidx; t < num_tiles; t += f.comm_ctas) {
+    int tm, tn;
+    tile_coords(p, t, tm, tn);
+    const int r0 = tm * BM;
+    const int64_t c0 = static_cast<int64_t>(tn) * (BN / 8);
+    const int rows = min(BM, p.M - r0);
+    const int64_t cleft = row_packs - c0;
+    const int cpk = cleft < BN / 8 ? static_cast<int>(cleft) : BN / 8;
+    const int owner = t % NG;
+    if (owner == f.rank) {
+      if (tid < NG && !wait_flag_reached(&f.sg.sig[tid]->tile_ready[t], f.epoch, f.status, f.limit_ns, f.rank, tid, 5))
+        fail = 1u;
+      __syncthreads();
+      if (fail) break;
+      for (int i = tid; i < rows * cpk; i += blockDim.x) {
+        const int r = i / cpk;
+        const int64_t off = static_cast<int64_t>(r0 + r) * row_packs + c0 + (i - r * cpk);
+        uint4 v[NG];
+#pragma unroll
+        for (int k = 0; k < NG; ++k) v[k] = ld_pack(reinterpret_cast<const uint4*>(rd.ptrs[k]) + off);
+#pragma unroll
+        for (int stride = 1; stride < NG; stride *= 2) {
+#pragma unroll
+          for (int k = 0; k + stride < NG; k += 2 * stride) v[k] = Elem<T>::add(v[k], v[k + stride]);
+        }
+        mine[off] = v[0];
+        out[static_cast<int64_t>(r0 + r) * out_row_packs + c0 + (i - r * cpk)] = v[0];
+      }
+      __syncthreads();
+      if (tid == 0) {
+        __threadfence_system();
+        st_flag_release(&self->tile_done[t], f.epoch);
+      }
+    } else {
+      if (tid == 0 && !wait_flag_reached(&f.sg.sig[owner]->tile_done[t], f.epoch, f.status, f.limit_ns, f.rank, owner, 6))
+        fail = 1u;
+      __syncthreads();
+      if (fail) break;
+      const uint4* src = reinterpret_cast<const uint4*>(rd.ptrs[owner]);
+      for (int i = tid; i < rows * cpk; i += blockDim.x) {
+        const int r = i / cpk;
+        const int64_t col = c0 + (i - r * cpk);
+        out[static_cast<int64_t>(r0 + r) * out_row_packs + col] = ld_pack(src + static_cast<int64_t>(r0 + r) * row_packs + col);
+      }
+    }
+  }
+  block_barrier<NG>(f.sg, self, f.rank, f.status, f.limit_ns, 7, &fail);
+}
+
+template <typename T, int BN>
+__device__ void comm_role(const GemmParams& p, int cidx) {
+  switch (p.f.world) {
+    case 2: comm_role_n<T, 2, BN>(p, cidx); break;
+    case 4: comm_role_n<T, 4, BN>(p, cidx); break;
+    case 8: comm_role_n<T, 8, BN>(p, cidx); break;
+    default: break;
+  }
+}
+
+template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR, bool FUSED = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
@@ -119,9 +215,17 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n;
   // scheduling unit: a CTA, or a pair of CTAs (cluster of 2) working on one 256-row tile
+  static_assert(!(FUSED && PAIR), "the fused variant is single-CTA");
+  const int gemm_ctas = FUSED ? static_cast<int>(gridDim.x) - p.f.comm_ctas : static_cast<int>(gridDim.x);
+  if constexpr (FUSED) {
+    if (static_cast<int>(blockIdx.x) >= gemm_ctas) {
+      comm_role<T, BN>(p, static_cast<int>(blockIdx.x) - gemm_ctas);
+      return;
+    }
+  }
   const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
   const int unit = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
-  const int num_units = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int num_units = PAIR ? gemm_ctas >> 1 : gemm_ctas;
   const bool leader = cta_rank == 0u;
 
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem_gen + C_::OFF_ABORT);
@@ -361,9 +465,22 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       epi_phase ^= 1u;
     };
+    int pending_tile = -1;  // fused: tile whose stores are in flight and whose "ready" flag is still to be raised
+    auto publish_pending = [&]() {
+      if constexpr (FUSED) {
+        if (epi_tid == 0 && pending_tile >= 0) {
+          bulk_wait_all();  // the tile's global writes are performed
+          __threadfence_system();
+          st_flag_release(&p.f.sg.sig[p.f.rank]->tile_ready[pending_tile], p.f.epoch);
+          pending_tile = -1;
+        }
+      }
+    };
     auto staging_release = [&]() {
       if (staging_busy) {
-        if (epi_tid == 0) bulk_wait_read_all();
+        if (epi_tid == 0) {
+          if constexpr (FUSED) publish_pending(); else bulk_wait_read_all();
+        }
         epi_sync();
         staging_busy = false;
       }
@@ -466,6 +583,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int b = 0; b < BN / 64; ++b) tma_store_2d(&tmap_c, sbase + b * (BM * 128), tn * BN + b * 64, row0);
             bulk_commit_group();
+            pending_tile = tile;
           }
           staging_busy = true;
         } else if (row < p.M) {
@@ -491,6 +609,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
     }
+    publish_pending();
     }  // draining warps
   }
 
@@ -559,14 +678,14 @@ int make_tmap(CUtensorMap* tm, int dtype, const void* base, int64_t rows, int64_
 
 __device__ uint32_t g_gemm_status[4];
 
-template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR>
+template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR, bool FUSED = false>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
            cudaStream_t stream) {
   using C_ = Cfg<BN, STAGES, SLEVELS, PAIR>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  auto kernel = tree_gemm_kernel<T, BN, STAGES, SLEVELS, PAIR>;
+  auto kernel = tree_gemm_kernel<T, BN, STAGES, SLEVELS, PAIR, FUSED>;
   if (dev < 64 && !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(C_::SMEM_BYTES));
@@ -792,6 +911,79 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
 
   if (dtype == TBIK_DTYPE_BF16) return launch_variant<__nv_bfloat16>(pl.tiling, pl.deep, ta, tb, tc, p, pl.grid, stream);
   return launch_variant<__half>(pl.tiling, pl.deep, ta, tb, tc, p, pl.grid, stream);
+}
+
+// ---------------------------------------------------------------- GEMM + tree all-reduce in one launch
+int gemm_launch_fused(const void* A, const void* W, void* part, int M, int N, int K, int64_t lda, int64_t ldw, int dtype,
+                      int leaf, void* workspace, size_t ws_bytes, const FusedArgs& fa, cudaStream_t stream) {
+  if (dtype != TBIK_DTYPE_BF16 && dtype != TBIK_DTYPE_FP16)
+    return set_error(TBIK_ERR_DTYPE, "fused GEMM + all-reduce supports bf16 and fp16");
+  if (fa.world != 2 && fa.world != 4 && fa.world != 8)
+    return set_error(TBIK_ERR_SHAPE, "fused GEMM + all-reduce supports 2, 4 or 8 ranks");
+  if (M <= 0 || N <= 0 || K <= 0 || N % 8 != 0 || fa.ldo % 8 != 0 || fa.ldo < N)
+    return set_error(TBIK_ERR_SHAPE, "fused GEMM + all-reduce: M, N, K > 0 and N, ldo multiples of 8");
+  if (leaf <= 0 || leaf % BK != 0) return set_error(TBIK_ERR_SHAPE, "leaf must be a positive multiple of 64");
+  int T, F, L;
+  if (tree_shape(K, leaf, &T, &F, &L) != TBIK_OK || L > 16)
+    return set_error(TBIK_ERR_SHAPE, "K must be a multiple of the leaf width (tree of at most 16 levels)");
+  if (!A || !W || !part || !fa.out) return set_error(TBIK_ERR_ARG, "fused GEMM + all-reduce: null pointer");
+  if (lda < K || ldw < K) return set_error(TBIK_ERR_SHAPE, "leading dimension smaller than the row");
+  if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(W) & 15u) || (lda % 8) || (ldw % 8) ||
+      (reinterpret_cast<uintptr_t>(part) & 15u) || (reinterpret_cast<uintptr_t>(fa.out) & 15u) ||
+      (workspace && (reinterpret_cast<uintptr_t>(workspace) & 15u)))
+    return set_error(TBIK_ERR_ALIGN, "fused GEMM + all-reduce: operands must be 16-byte aligned, strides multiples of 8");
+  const int sms = sm_count();
+  int comm = fa.comm_ctas;
+  if (comm < 2 || comm > sms / 2) return set_error(TBIK_ERR_ARG, "fused GEMM + all-reduce: comm_ctas out of range");
+  const Plan pl = make_plan(3, M, N, L, sms - comm);
+  if (pl.tiles_m * pl.tiles_n > kMaxTiles) return set_error(TBIK_ERR_SHAPE, "fused GEMM + all-reduce: too many output tiles");
+  if (pl.scratch_bytes > 0 && (workspace == nullptr || pl.scratch_bytes > ws_bytes))
+    return set_error(TBIK_ERR_SHAPE, "fused GEMM + all-reduce: scratch buffer too small for this tree");
+  const Variant& v = kVariants[2][0];
+  CUtensorMap ta, tb, tc;
+  int rc = make_tmap(&ta, dtype, A, M, K, lda, BM);
+  if (rc != TBIK_OK) return rc;
+  rc = make_tmap(&tb, dtype, W, N, K, ldw, v.bn);
+  if (rc != TBIK_OK) return rc;
+  rc = make_tmap(&tc, dtype, part, M, N, N, BM);
+  if (rc != TBIK_OK) return rc;
+  GemmParams p{};
+  p.C = part;
+  p.ldc = N;
+  p.M = M;
+  p.N = N;
+  p.kblocks_per_leaf = leaf / BK;
+  p.T = T;
+  p.F = F;
+  p.L = L;
+  p.tiles_m = pl.tiles_m;
+  p.tiles_n = pl.tiles_n;
+  p.group_m = 16;
+  p.scratch = static_cast<uint32_t*>(workspace);
+  p.scratch_levels = pl.scratch_levels;
+  p.tma_store = 1;
+  void* status_ptr = nullptr;
+  cudaGetSymbolAddress(&status_ptr, g_gemm_status);
+  p.status = static_cast<uint32_t*>(status_ptr);
+  p.f.rd = static_cast<const RankData*>(fa.rank_data_slot);
+  for (int i = 0; i < fa.world; ++i) p.f.sg.sig[i] = static_cast<Signal*>(fa.signals[i]);
+  p.f.status = static_cast<ArStatus*>(fa.status_dev);
+  p.f.limit_ns = fa.wait_limit_ns;
+  p.f.world = fa.world;
+  p.f.rank = fa.rank;
+  p.f.comm_ctas = comm;
+  p.f.epoch = fa.epoch;
+  p.f.out = fa.out;
+  p.f.ldo = fa.ldo;
+  const int grid = pl.grid + comm;
+  if (dtype == TBIK_DTYPE_BF16) return launch<__nv_bfloat16, 256, 3, 1, false, true>(ta, tb, tc, p, grid, stream);
+  return launch<__half, 256, 3, 1, false, true>(ta, tb, tc, p, grid, stream);
+}
+
+size_t gemm_fused_workspace_bytes(int M, int N, int64_t K, int leaf) {
+  int T, F, L;
+  if (M <= 0 || N <= 0 || tree_shape(K, leaf, &T, &F, &L) != TBIK_OK) return 0;
+  return make_plan(3, M, N, L, 0).scratch_bytes;
 }
 
 // ---------------------------------------------------------------- the entry point that allocates nothing

@@ -55,6 +55,12 @@ def register_graph_buffers(fa: int, handles: List[List[int]], offsets: List[List
     _custom_ar.register_graph_buffers(fa, handles, offsets)
 
 
+def tree_matmul_allreduce(fa: int, A: torch.Tensor, B: torch.Tensor, reg_buffer: int, reg_buffer_sz_bytes: int,
+                          comm_ctas: int = 0) -> torch.Tensor:
+    """Row-split GEMM and tree all-reduce in one kernel launch (addition of this implementation)."""
+    return _custom_ar.tree_matmul_allreduce(fa, A, B, reg_buffer, reg_buffer_sz_bytes, comm_ctas)
+
+
 # keys of `configure`
 CFG_SCRATCH_BYTES, CFG_ONESHOT_MAX_BYTES, CFG_MAX_BLOCKS, CFG_WAIT_LIMIT_NS = 1, 2, 3, 4
 

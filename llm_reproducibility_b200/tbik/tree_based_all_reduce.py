@@ -40,14 +40,19 @@ def tree_all_reduce_sum(x: torch.Tensor, device_group=None) -> torch.Tensor:
 def tree_matmul_all_reduce(A: torch.Tensor, B: torch.Tensor, device_group=None) -> torch.Tensor:
     """Row-split layer in one call: this rank's tree matmul, then the tree all-reduce.
 
-    Same bits as `tree_all_reduce_sum(matmul_tp_persistent(A, B), group)`.  When the peer-to-peer
-    communicator is usable the GEMM writes its partial result directly into the IPC-registered
-    buffer the peers read from, so no staging copy is made."""
+    Same bits as `tree_all_reduce_sum(matmul_tp_persistent(A, B), group)`.  Preferred path: one fused
+    kernel (`CustomTreeAllreduce.matmul_tree_all_reduce`; $TBIK_FUSED=0 turns it off).  Otherwise, when the
+    peer-to-peer communicator is usable, the GEMM writes its partial result directly into the
+    IPC-registered buffer the peers read from, so no staging copy is made."""
     global custom_ar
     from .tree_based_matmul import matmul_tp_persistent
     if custom_ar is None:
         from ..mini_allreduce import CustomTreeAllreduce
         custom_ar = CustomTreeAllreduce(group=device_group, device=A.device, max_size=_max_size())
+    if not custom_ar.disabled and os.environ.get("TBIK_FUSED", "1") != "0":
+        y = custom_ar.matmul_tree_all_reduce(A, B)  # GEMM and all-reduce overlapped in one kernel
+        if y is not None:
+            return y
     view = None
     capturing = A.is_cuda and torch.cuda.is_current_stream_capturing()
     if not custom_ar.disabled and not custom_ar._IS_CAPTURING and not capturing:

@@ -53,6 +53,14 @@ def _workspace(device: torch.device, stream: int, nbytes: int) -> Optional[torch
     return ws
 
 
+def prepare_operands(A: torch.Tensor, B: torch.Tensor):
+    """(A', W) in the layout the kernels take: A' row-major with aligned rows, W = B^T with K contiguous."""
+    M, K = A.shape
+    if A.stride(1) != 1 or A.stride(0) % 8 != 0 or A.data_ptr() % 16 != 0 or (M > 1 and A.stride(0) < K):
+        A = A.contiguous()
+    return A, _k_major_weight(B)
+
+
 def matmul_tp_persistent(A: torch.Tensor, B: torch.Tensor, bias: Optional[torch.Tensor] = None,
                          *, leaf: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C = A @ B with the K reduction in the fixed tree order; returns a new [M, N] tensor of A's dtype.

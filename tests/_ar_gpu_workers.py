@@ -1,4 +1,6 @@
 """Per-rank bodies of the multi-GPU all-reduce tests (imported by spawned processes)."""
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -163,6 +165,27 @@ def dispatcher(rank, world):
         want = matmul_tp_persistent(X2, W2.t())
         torch.cuda.synchronize()
         assert torch.equal(bits(got), bits(want)), (K2, N2)
+        # the fused kernel against the two-kernel composition, and with other comm-CTA counts
+        os.environ["TBIK_FUSED"] = "0"
+        unfused = tar.tree_matmul_all_reduce(X2[:, rank * k2:(rank + 1) * k2], W2[:, rank * k2:(rank + 1) * k2].t(), None)
+        os.environ["TBIK_FUSED"] = "1"
+        assert torch.equal(bits(unfused), bits(want))
+        for cc in (2, 8, 40):
+            y = tar.custom_ar.matmul_tree_all_reduce(X2[:, rank * k2:(rank + 1) * k2], W2[:, rank * k2:(rank + 1) * k2].t(), cc)
+            torch.cuda.synchronize()
+            tar.custom_ar.check_status()
+            assert y is not None and torch.equal(bits(y), bits(want)), (K2, N2, cc)
+    # ragged sizes through the fused kernel (edge tiles in M and N), repeated calls reuse the tile flags
+    g3 = torch.Generator(device=device).manual_seed(5)
+    X3 = torch.randn(300, 2048, generator=g3, device=device).to(torch.bfloat16)
+    W3 = (torch.randn(520, 2048, generator=g3, device=device) * 0.05).to(torch.bfloat16)
+    k3 = 2048 // world
+    want3 = matmul_tp_persistent(X3, W3.t())
+    for _ in range(4):
+        y = tar.custom_ar.matmul_tree_all_reduce(X3[:, rank * k3:(rank + 1) * k3], W3[:, rank * k3:(rank + 1) * k3].t())
+        torch.cuda.synchronize()
+        assert y is not None and torch.equal(bits(y), bits(want3))
+    tar.custom_ar.check_status()
     dist.barrier()
     tar.reset_communicator()
     return True
