@@ -22,6 +22,7 @@ size_t gemm_static_scratch_bytes();
 // What the GEMM kernel needs from a communicator to reduce its own output tiles over peer memory.
 struct FusedArgs {
   const void* rank_data_slot;  // device record with every rank's address of the registered partial buffer
+  const void* peer_parts[8];   // the same addresses on the host: rank k's partial buffer as mapped in this process
   void* signals[8];            // every rank's meta buffer (flag area), as mapped in this process
   void* status_dev;            // host-mapped status word (device address)
   unsigned long long wait_limit_ns;

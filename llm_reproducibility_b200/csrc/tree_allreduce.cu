@@ -146,6 +146,7 @@ struct Communicator {
   RankData* rd_next = nullptr;  // next free slot of the caller-owned device table
   RankData* rd_end = nullptr;
   std::unordered_map<const void*, RankData*> registered;
+  std::unordered_map<const void*, RankData> registered_host;  // host copies of the records (for tensor maps)
   std::vector<void*> graph_pending;  // inputs seen during stream capture, slots reserved in order
   std::map<IpcKey, char*> opened;
   size_t scratch_bytes = 8u << 20;
@@ -292,6 +293,8 @@ int ar_gemm_tree_allreduce(tbik_ar_t h, const void* A, const void* W, void* out,
   if (it == c->registered.end()) return set_error(TBIK_ERR_STATE, "fused GEMM + all-reduce: buffer is not registered!");
   FusedArgs fa{};
   fa.rank_data_slot = it->second;
+  const RankData& host_rd = c->registered_host[reg_buffer];
+  for (int i = 0; i < c->world; ++i) fa.peer_parts[i] = host_rd.ptrs[i];
   for (int i = 0; i < c->world; ++i) fa.signals[i] = c->sg.sig[i];
   fa.status_dev = c->status_dev;
   fa.wait_limit_ns = c->wait_limit_ns;
@@ -378,6 +381,7 @@ int ar_register_buffer(tbik_ar_t h, void* const* ptrs) {
   cudaError_t e = cudaMemcpy(c->rd_next, &d, sizeof(d), cudaMemcpyHostToDevice);
   if (e != cudaSuccess) return set_cuda_error(e, "cudaMemcpy(rank data)");
   c->registered[ptrs[c->rank]] = c->rd_next;
+  c->registered_host[ptrs[c->rank]] = d;
   ++c->rd_next;
   return TBIK_OK;
 }

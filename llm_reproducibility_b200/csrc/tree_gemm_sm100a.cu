@@ -124,13 +124,47 @@ TBIK_DEVICE void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
 // levels of the same reduction tree the GEMM started), writes the sum over its own partial tile and
 // into its result, and publishes "done"; every other rank then copies the owner's tile into its own
 // result.  Tiles are visited in the order the GEMM CTAs produce them, so the NVLink traffic of a tile
-// overlaps the UMMAs of later tiles.  All waits are bounded; the final barrier keeps every rank's
-// buffers untouched until all ranks have finished reading.
+// overlaps the UMMAs of later tiles.
+//
+// Peer data is pulled with tiled TMA loads (one destination CTA, peer memory as the source) into two
+// 64 KiB shared-memory buffers: the TMA unit keeps far more bytes in flight per SM than load
+// instructions can, which is what NVLink latency needs.  A job is one box column-block of an owned tile
+// (n loads, one per rank) or a whole tile to copy from its owner.  The next job is issued before the
+// current one is consumed only if its flags are already up, so a communication CTA never blocks on
+// another one while holding work that the other needs.  All waits are bounded; the final barrier keeps
+// every rank's buffers untouched until all ranks have finished reading.
+struct PeerMaps {
+  CUtensorMap m[8];  // rank k's partial-result buffer, box = 64 columns x (128 or 64) rows
+};
+
+constexpr uint32_t COMM_BUF_BYTES = 65536;
+constexpr int COMM_BUFS = 3;  // 192 KiB of loads in flight per communication CTA
+
 template <typename T, int NG, int BN>
-__device__ void comm_role_n(const GemmParams& p, int cidx) {
+__device__ void comm_role_n(const GemmParams& p, const PeerMaps& maps, int cidx) {
+  static_assert(BN == 256, "communication role is written for 128x256 tiles");
+  constexpr int BOX_ROWS = NG == 8 ? 64 : 128;              // rows per 64-column box
+  constexpr uint32_t BOXB = BOX_ROWS * 128;                   // bytes of one box
+  constexpr int TILE_BOXES = (BM / BOX_ROWS) * (BN / 64);     // boxes of one tile (4 or 8), exactly one buffer
+  constexpr int OWN_BOXES = COMM_BUF_BYTES / (NG * BOXB);     // boxes (per rank) one "reduce" job covers
+  constexpr int OWN_JOBS = TILE_BOXES / OWN_BOXES;            // jobs per owned tile
+  static_assert(TILE_BOXES * BOXB == COMM_BUF_BYTES && OWN_BOXES >= 1 && OWN_JOBS * OWN_BOXES == TILE_BOXES, "buffer plan");
+  extern __shared__ uint8_t smem_raw[];
   __shared__ uint32_t fail;
+  __shared__ uint32_t inflight_s;
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
+  const uint32_t bar0 = sbase + COMM_BUFS * COMM_BUF_BYTES;
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(sgen + COMM_BUFS * COMM_BUF_BYTES + 64);
   const FusedDev& f = p.f;
-  if (threadIdx.x == 0) fail = 0u;
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    fail = 0u;
+    inflight_s = 0u;
+    *abort_flag = 0u;
+    for (int i = 0; i < COMM_BUFS; ++i) mbar_init(bar0 + 8u * i, 1);
+    fence_mbar_init();
+  }
   __syncthreads();
   const RankData rd = *f.rd;
   Signal* self = f.sg.sig[f.rank];
@@ -139,70 +173,155 @@ __device__ void comm_role_n(const GemmParams& p, int cidx) {
   const int64_t out_row_packs = f.ldo / 8;
   uint4* out = reinterpret_cast<uint4*>(f.out);
   uint4* mine = reinterpret_cast<uint4*>(const_cast<void*>(rd.ptrs[f.rank]));
-  const int tid = threadIdx.x;
-  for (int t = cidx; t < num_tiles; t += f.comm_ctas) {
-    int tm, tn;
+
+  // job = (tile, sub): an owned tile is OWN_JOBS jobs, a tile to copy from its owner is one job
+  auto owned = [&](int t) { return t % NG == f.rank; };
+  auto advance = [&](int& t, int& sub) {
+    if (owned(t) && sub + 1 < OWN_JOBS) {
+      ++sub;
+    } else {
+      t += f.comm_ctas;
+      sub = 0;
+    }
+  };
+  auto box_xy = [&](int tm, int tn, int box, int& x, int& y) {
+    x = tn * BN + (box % (BN / 64)) * 64;
+    y = tm * BM + (box / (BN / 64)) * BOX_ROWS;
+  };
+  // thread 0: are the flags this job needs up?  block = wait for them (bounded)
+  auto flags_up = [&](int t, int sub, bool block) -> bool {
+    if (owned(t)) {
+      if (sub != 0) return true;  // checked with the tile's first job
+      for (int k = 0; k < NG; ++k) {
+        const uint32_t* fl = &f.sg.sig[k]->tile_ready[t];
+        if (block) {
+          if (!wait_flag_reached(fl, f.epoch, f.status, f.limit_ns, f.rank, k, 5)) return false;
+        } else if (static_cast<int32_t>(ld_flag_acquire(fl) - f.epoch) < 0) {
+          return false;
+        }
+      }
+      return true;
+    }
+    const int o = t % NG;
+    const uint32_t* fl = &f.sg.sig[o]->tile_done[t];
+    if (block) return wait_flag_reached(fl, f.epoch, f.status, f.limit_ns, f.rank, o, 6);
+    return static_cast<int32_t>(ld_flag_acquire(fl) - f.epoch) >= 0;
+  };
+  // thread 0: start the TMA loads of a job into buffer `slot`
+  auto issue = [&](int t, int sub, int slot) {
+    int tm, tn, x, y;
     tile_coords(p, t, tm, tn);
-    const int r0 = tm * BM;
-    const int64_t c0 = static_cast<int64_t>(tn) * (BN / 8);
-    const int rows = min(BM, p.M - r0);
-    const int64_t cleft = row_packs - c0;
-    const int cpk = cleft < BN / 8 ? static_cast<int>(cleft) : BN / 8;
-    const int owner = t % NG;
-    if (owner == f.rank) {
-      if (tid < NG && !wait_flag_reached(&f.sg.sig[tid]->tile_ready[t], f.epoch, f.status, f.limit_ns, f.rank, tid, 5))
-        fail = 1u;
-      __syncthreads();
-      if (fail) break;
-      for (int i = tid; i < rows * cpk; i += blockDim.x) {
-        const int r = i / cpk;
-        const int64_t off = static_cast<int64_t>(r0 + r) * row_packs + c0 + (i - r * cpk);
+    const uint32_t dst = sbase + slot * COMM_BUF_BYTES;
+    const uint32_t bar = bar0 + 8u * slot;
+    asm volatile("fence.proxy.async;" ::: "memory");  // flags were read by loads; the data is read by the TMA unit
+    mbar_arrive_expect_tx(bar, COMM_BUF_BYTES);
+    if (owned(t)) {
+#pragma unroll
+      for (int ob = 0; ob < OWN_BOXES; ++ob) {
+        box_xy(tm, tn, sub * OWN_BOXES + ob, x, y);
+#pragma unroll
+        for (int k = 0; k < NG; ++k) tma_load_2d(dst + (ob * NG + k) * BOXB, &maps.m[k], x, y, bar);
+      }
+    } else {
+#pragma unroll
+      for (int bx = 0; bx < TILE_BOXES; ++bx) {
+        box_xy(tm, tn, bx, x, y);
+        tma_load_2d(dst + bx * BOXB, &maps.m[t % NG], x, y, bar);
+      }
+    }
+  };
+
+  int it = cidx, isub = 0, islot = 0;  // next job to issue (meaningful in thread 0)
+  int ct = cidx, csub = 0, cslot = 0;  // next job to consume (all threads)
+  uint32_t inflight = 0;               // thread 0's count of issued, not yet consumed jobs
+  uint32_t phases = 0;                 // bit s = parity to wait for on buffer s
+  while (true) {
+    if (tid == 0) {
+      // fill the ring; only block on flags when nothing is in flight, so that no communication CTA
+      // ever holds back work another one is waiting for
+      while (inflight < COMM_BUFS && it < num_tiles) {
+        const bool block = inflight == 0;
+        if (!flags_up(it, isub, block)) {
+          if (block) fail = 1u;
+          break;
+        }
+        issue(it, isub, islot);
+        advance(it, isub);
+        islot = islot + 1 == COMM_BUFS ? 0 : islot + 1;
+        ++inflight;
+      }
+      inflight_s = inflight;
+    }
+    __syncthreads();
+    if (fail != 0u || inflight_s == 0u) break;
+    if (!mbar_wait_bounded(bar0 + 8u * cslot, (phases >> cslot) & 1u, abort_flag, f.limit_ns)) fail = 1u;
+    phases ^= 1u << cslot;
+    __syncthreads();
+    if (fail != 0u) break;
+    // ---- consume the job in buffer cslot
+    int tm, tn;
+    tile_coords(p, ct, tm, tn);
+    const uint4* buf = reinterpret_cast<const uint4*>(sgen + cslot * COMM_BUF_BYTES);
+    if (owned(ct)) {
+      for (int i = tid; i < OWN_BOXES * BOX_ROWS * 8; i += blockDim.x) {
+        const int ob = i / (BOX_ROWS * 8), j = i - ob * (BOX_ROWS * 8);
         uint4 v[NG];
 #pragma unroll
-        for (int k = 0; k < NG; ++k) v[k] = ld_pack(reinterpret_cast<const uint4*>(rd.ptrs[k]) + off);
+        for (int k = 0; k < NG; ++k) v[k] = buf[(ob * NG + k) * (BOXB / 16) + j];
 #pragma unroll
         for (int stride = 1; stride < NG; stride *= 2) {
 #pragma unroll
           for (int k = 0; k + stride < NG; k += 2 * stride) v[k] = Elem<T>::add(v[k], v[k + stride]);
         }
-        mine[off] = v[0];
-        out[static_cast<int64_t>(r0 + r) * out_row_packs + c0 + (i - r * cpk)] = v[0];
-      }
-      __syncthreads();
-      if (tid == 0) {
-        __threadfence_system();
-        st_flag_release(&self->tile_done[t], f.epoch);
+        int x, y;
+        box_xy(tm, tn, csub * OWN_BOXES + ob, x, y);
+        const int r = y + (j >> 3);
+        const int64_t c = x / 8 + (j & 7);
+        if (r < p.M && c < row_packs) {
+          mine[static_cast<int64_t>(r) * row_packs + c] = v[0];
+          out[static_cast<int64_t>(r) * out_row_packs + c] = v[0];
+        }
       }
     } else {
-      if (tid == 0 && !wait_flag_reached(&f.sg.sig[owner]->tile_done[t], f.epoch, f.status, f.limit_ns, f.rank, owner, 6))
-        fail = 1u;
-      __syncthreads();
-      if (fail) break;
-      const uint4* src = reinterpret_cast<const uint4*>(rd.ptrs[owner]);
-      for (int i = tid; i < rows * cpk; i += blockDim.x) {
-        const int r = i / cpk;
-        const int64_t col = c0 + (i - r * cpk);
-        out[static_cast<int64_t>(r0 + r) * out_row_packs + col] = ld_pack(src + static_cast<int64_t>(r0 + r) * row_packs + col);
+      for (int i = tid; i < TILE_BOXES * BOX_ROWS * 8; i += blockDim.x) {
+        const int bx = i / (BOX_ROWS * 8), j = i - bx * (BOX_ROWS * 8);
+        int x, y;
+        box_xy(tm, tn, bx, x, y);
+        const int r = y + (j >> 3);
+        const int64_t c = x / 8 + (j & 7);
+        if (r < p.M && c < row_packs) out[static_cast<int64_t>(r) * out_row_packs + c] = buf[i];
       }
     }
+    __syncthreads();  // the buffer is free again; this rank's stores of the job are issued
+    if (tid == 0) {
+      if (owned(ct) && csub == OWN_JOBS - 1) {
+        __threadfence_system();
+        st_flag_release(&self->tile_done[ct], f.epoch);
+      }
+      --inflight;
+    }
+    advance(ct, csub);
+    cslot = cslot + 1 == COMM_BUFS ? 0 : cslot + 1;
   }
   block_barrier<NG>(f.sg, self, f.rank, f.status, f.limit_ns, 7, &fail);
 }
 
 template <typename T, int BN>
-__device__ void comm_role(const GemmParams& p, int cidx) {
-  switch (p.f.world) {
-    case 2: comm_role_n<T, 2, BN>(p, cidx); break;
-    case 4: comm_role_n<T, 4, BN>(p, cidx); break;
-    case 8: comm_role_n<T, 8, BN>(p, cidx); break;
-    default: break;
+__device__ void comm_role(const GemmParams& p, const PeerMaps& maps, int cidx) {
+  if constexpr (BN == 256) {
+    switch (p.f.world) {
+      case 2: comm_role_n<T, 2, BN>(p, maps, cidx); break;
+      case 4: comm_role_n<T, 4, BN>(p, maps, cidx); break;
+      case 8: comm_role_n<T, 8, BN>(p, maps, cidx); break;
+      default: break;
+    }
   }
 }
 
 template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR, bool FUSED = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_c, const GemmParams p, const __grid_constant__ PeerMaps peers) {
   using C_ = Cfg<BN, STAGES, SLEVELS, PAIR>;
   constexpr uint32_t STAGE_BYTES = C_::STAGE_BYTES;
   constexpr int TILE_M = C_::TILE_M;
@@ -219,7 +338,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int gemm_ctas = FUSED ? static_cast<int>(gridDim.x) - p.f.comm_ctas : static_cast<int>(gridDim.x);
   if constexpr (FUSED) {
     if (static_cast<int>(blockIdx.x) >= gemm_ctas) {
-      comm_role<T, BN>(p, static_cast<int>(blockIdx.x) - gemm_ctas);
+      comm_role<T, BN>(p, peers, static_cast<int>(blockIdx.x) - gemm_ctas);
       return;
     }
   }
@@ -656,7 +775,7 @@ EncodeTiledFn get_encode_fn() {
 
 // Row-major [rows, K] 16-bit matrix, row stride `ld` elements, box = 64 (K) x `box_rows` rows.
 int make_tmap(CUtensorMap* tm, int dtype, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows,
-              bool quiet = false) {
+              bool quiet = false, bool swizzle = true) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return set_error(TBIK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
@@ -665,7 +784,8 @@ int make_tmap(CUtensorMap* tm, int dtype, const void* base, int64_t rows, int64_
   cuuint32_t estr[2] = {1, 1};
   CUtensorMapDataType dt = dtype == TBIK_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = fn(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     if (quiet) return TBIK_ERR_CUDA;
     char msg[160];
@@ -680,7 +800,9 @@ __device__ uint32_t g_gemm_status[4];
 
 template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR, bool FUSED = false>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
-           cudaStream_t stream) {
+           cudaStream_t stream, const PeerMaps* peers = nullptr) {
+  static const PeerMaps no_peers{};
+  const PeerMaps& pm = peers ? *peers : no_peers;
   using C_ = Cfg<BN, STAGES, SLEVELS, PAIR>;
   static bool configured[64] = {};
   int dev = 0;
@@ -705,10 +827,10 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, p, pm);
     if (e != cudaSuccess) return set_cuda_error(e, "tree_gemm_kernel launch");
   } else {
-    kernel<<<grid, NUM_THREADS, C_::SMEM_BYTES, stream>>>(ta, tb, tc, p);
+    kernel<<<grid, NUM_THREADS, C_::SMEM_BYTES, stream>>>(ta, tb, tc, p, pm);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return set_cuda_error(e, "tree_gemm_kernel launch");
   }
@@ -975,9 +1097,14 @@ int gemm_launch_fused(const void* A, const void* W, void* part, int M, int N, in
   p.f.epoch = fa.epoch;
   p.f.out = fa.out;
   p.f.ldo = fa.ldo;
+  PeerMaps pm{};
+  for (int k = 0; k < fa.world; ++k) {
+    rc = make_tmap(&pm.m[k], dtype, fa.peer_parts[k], M, N, N, fa.world == 8 ? 64 : 128, false, /*swizzle=*/false);
+    if (rc != TBIK_OK) return rc;
+  }
   const int grid = pl.grid + comm;
-  if (dtype == TBIK_DTYPE_BF16) return launch<__nv_bfloat16, 256, 3, 1, false, true>(ta, tb, tc, p, grid, stream);
-  return launch<__half, 256, 3, 1, false, true>(ta, tb, tc, p, grid, stream);
+  if (dtype == TBIK_DTYPE_BF16) return launch<__nv_bfloat16, 256, 3, 1, false, true>(ta, tb, tc, p, grid, stream, &pm);
+  return launch<__half, 256, 3, 1, false, true>(ta, tb, tc, p, grid, stream, &pm);
 }
 
 size_t gemm_fused_workspace_bytes(int M, int N, int64_t K, int leaf) {

@@ -40,16 +40,18 @@ def tree_all_reduce_sum(x: torch.Tensor, device_group=None) -> torch.Tensor:
 def tree_matmul_all_reduce(A: torch.Tensor, B: torch.Tensor, device_group=None) -> torch.Tensor:
     """Row-split layer in one call: this rank's tree matmul, then the tree all-reduce.
 
-    Same bits as `tree_all_reduce_sum(matmul_tp_persistent(A, B), group)`.  Preferred path: one fused
-    kernel (`CustomTreeAllreduce.matmul_tree_all_reduce`; $TBIK_FUSED=0 turns it off).  Otherwise, when the
-    peer-to-peer communicator is usable, the GEMM writes its partial result directly into the
-    IPC-registered buffer the peers read from, so no staging copy is made."""
+    Same bits as `tree_all_reduce_sum(matmul_tp_persistent(A, B), group)`.  Default: the GEMM writes its
+    partial result directly into the IPC-registered buffer the peers read from (no staging copy), then the
+    tree all-reduce kernel runs.  With $TBIK_FUSED=1 the single fused kernel is used instead
+    (`CustomTreeAllreduce.matmul_tree_all_reduce`): same bits; on the measured B200s one SM pulls only
+    about 12-15 GB/s over NVLink, so the communication CTAs it takes from the GEMM cost more than the
+    overlap returns, which is why it is not the default."""
     global custom_ar
     from .tree_based_matmul import matmul_tp_persistent
     if custom_ar is None:
         from ..mini_allreduce import CustomTreeAllreduce
         custom_ar = CustomTreeAllreduce(group=device_group, device=A.device, max_size=_max_size())
-    if not custom_ar.disabled and os.environ.get("TBIK_FUSED", "1") != "0":
+    if not custom_ar.disabled and os.environ.get("TBIK_FUSED", "0") == "1":
         y = custom_ar.matmul_tree_all_reduce(A, B)  # GEMM and all-reduce overlapped in one kernel
         if y is not None:
             return y

@@ -166,10 +166,10 @@ def dispatcher(rank, world):
         torch.cuda.synchronize()
         assert torch.equal(bits(got), bits(want)), (K2, N2)
         # the fused kernel against the two-kernel composition, and with other comm-CTA counts
-        os.environ["TBIK_FUSED"] = "0"
-        unfused = tar.tree_matmul_all_reduce(X2[:, rank * k2:(rank + 1) * k2], W2[:, rank * k2:(rank + 1) * k2].t(), None)
         os.environ["TBIK_FUSED"] = "1"
-        assert torch.equal(bits(unfused), bits(want))
+        fused = tar.tree_matmul_all_reduce(X2[:, rank * k2:(rank + 1) * k2], W2[:, rank * k2:(rank + 1) * k2].t(), None)
+        os.environ["TBIK_FUSED"] = "0"
+        assert torch.equal(bits(fused), bits(want))
         for cc in (2, 8, 40):
             y = tar.custom_ar.matmul_tree_all_reduce(X2[:, rank * k2:(rank + 1) * k2], W2[:, rank * k2:(rank + 1) * k2].t(), cc)
             torch.cuda.synchronize()
