@@ -120,6 +120,7 @@ typedef void* tbik_ar_t;
 #define TBIK_AR_CFG_ONESHOT_MAX_BYTES 2 /* messages up to this size use the one-shot schedule (0 = built-in) */
 #define TBIK_AR_CFG_MAX_BLOCKS 3        /* upper bound on CTAs per launch (0 = built-in)               */
 #define TBIK_AR_CFG_WAIT_LIMIT_NS 4     /* bound of one cross-GPU barrier wait                          */
+#define TBIK_AR_CFG_THREADS 5           /* threads per CTA, a multiple of 32 in [32, 512] (0 = built-in) */
 
 /* Size in bytes of the signal (flag) area at the start of every rank's meta buffer.
  * Replaces: meta_size, mini_allreduce/tbik_kernel/csrc/allreduce/custom_all_reduce.cu:148-150. */

@@ -152,6 +152,7 @@ struct Communicator {
   size_t scratch_bytes = 8u << 20;
   size_t oneshot_max_bytes = 0;  // 0 = built-in policy
   int max_blocks = 0;            // 0 = built-in policy
+  int threads = 0;               // 0 = built-in policy
   uint64_t wait_limit_ns = kArWaitLimitNs;
   ArStatus* status_host = nullptr;
   ArStatus* status_dev = nullptr;
@@ -164,12 +165,12 @@ static Communicator* as_comm(tbik_ar_t h) { return reinterpret_cast<Communicator
 
 template <typename T, int NG, bool TREE>
 static int launch_ar(Communicator* c, const RankData* slot, void* out, int64_t npacks, bool twoshot, int blocks,
-                     cudaStream_t stream) {
+                     int threads, cudaStream_t stream) {
   if (twoshot)
-    allreduce_twoshot_kernel<T, NG, TREE><<<blocks, kThreads, 0, stream>>>(slot, c->sg, c->self, out, c->rank, npacks,
+    allreduce_twoshot_kernel<T, NG, TREE><<<blocks, threads, 0, stream>>>(slot, c->sg, c->self, out, c->rank, npacks,
                                                                             c->status_dev, c->wait_limit_ns);
   else
-    allreduce_oneshot_kernel<T, NG, TREE><<<blocks, kThreads, 0, stream>>>(slot, c->sg, c->self, out, c->rank, npacks,
+    allreduce_oneshot_kernel<T, NG, TREE><<<blocks, threads, 0, stream>>>(slot, c->sg, c->self, out, c->rank, npacks,
                                                                             c->status_dev, c->wait_limit_ns);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_cuda_error(e, "all-reduce kernel launch");
@@ -178,17 +179,17 @@ static int launch_ar(Communicator* c, const RankData* slot, void* out, int64_t n
 
 template <typename T, bool TREE>
 static int dispatch_world(Communicator* c, const RankData* slot, void* out, int64_t npacks, bool twoshot, int blocks,
-                          cudaStream_t stream) {
+                          int threads, cudaStream_t stream) {
   switch (c->world) {
     case 1:
-      if constexpr (TREE) return launch_ar<T, 1, TREE>(c, slot, out, npacks, false, blocks, stream);
+      if constexpr (TREE) return launch_ar<T, 1, TREE>(c, slot, out, npacks, false, blocks, threads, stream);
       break;
-    case 2: return launch_ar<T, 2, TREE>(c, slot, out, npacks, twoshot, blocks, stream);
-    case 4: return launch_ar<T, 4, TREE>(c, slot, out, npacks, twoshot, blocks, stream);
+    case 2: return launch_ar<T, 2, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream);
+    case 4: return launch_ar<T, 4, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream);
     case 6:
-      if constexpr (!TREE) return launch_ar<T, 6, TREE>(c, slot, out, npacks, twoshot, blocks, stream);
+      if constexpr (!TREE) return launch_ar<T, 6, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream);
       break;
-    case 8: return launch_ar<T, 8, TREE>(c, slot, out, npacks, twoshot, blocks, stream);
+    case 8: return launch_ar<T, 8, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream);
     default: break;
   }
   return set_error(TBIK_ERR_SHAPE, TREE ? "tree all-reduce supports 1, 2, 4 or 8 ranks"
@@ -246,7 +247,8 @@ int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, vo
   const int64_t npacks = static_cast<int64_t>(bytes / 16);
   size_t one_max = c->oneshot_max_bytes;
   // two ranks: both schedules pull the same number of remote bytes, one-shot skips the scratch round trip
-  if (one_max == 0) one_max = c->world <= 2 ? ~size_t(0) : (c->world <= 4 ? (512u << 10) : (256u << 10));
+  // more ranks: measured on 8 GPUs, one-shot wins up to 1 MiB (26 vs 37 us at 512 KiB, 32 vs 38 us at 1 MiB), loses from 2 MiB
+  if (one_max == 0) one_max = c->world <= 2 ? ~size_t(0) : (1u << 20);
   bool twoshot = c->world > 1 && bytes > one_max && c->full_nvlink;
   if (twoshot) {
     const int64_t part = npacks / c->world + npacks % c->world;
@@ -256,21 +258,22 @@ int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, vo
     }
   }
   const int64_t work = twoshot ? (npacks + c->world - 1) / c->world : npacks;
-  int cap_blocks = c->max_blocks > 0 ? c->max_blocks : (bytes <= (512u << 10) ? 36 : c->sm_count);
+  int cap_blocks = c->max_blocks > 0 ? c->max_blocks : (bytes <= (256u << 10) ? 36 : c->sm_count);
   if (cap_blocks > kMaxBlocks) cap_blocks = kMaxBlocks;
   if (cap_blocks > c->sm_count) cap_blocks = c->sm_count;
-  int blocks = static_cast<int>((work + kThreads - 1) / kThreads);
+  const int threads = c->threads > 0 ? c->threads : kThreads;
+  int blocks = static_cast<int>((work + threads - 1) / threads);
   if (blocks > cap_blocks) blocks = cap_blocks;
   if (blocks < 1) blocks = 1;
 
   if (dtype == TBIK_DTYPE_FP32)
-    return tree ? dispatch_world<float, true>(c, slot, out, npacks, twoshot, blocks, stream)
-                : dispatch_world<float, false>(c, slot, out, npacks, twoshot, blocks, stream);
+    return tree ? dispatch_world<float, true>(c, slot, out, npacks, twoshot, blocks, threads, stream)
+                : dispatch_world<float, false>(c, slot, out, npacks, twoshot, blocks, threads, stream);
   if (dtype == TBIK_DTYPE_FP16)
-    return tree ? dispatch_world<__half, true>(c, slot, out, npacks, twoshot, blocks, stream)
-                : dispatch_world<__half, false>(c, slot, out, npacks, twoshot, blocks, stream);
-  return tree ? dispatch_world<__nv_bfloat16, true>(c, slot, out, npacks, twoshot, blocks, stream)
-              : dispatch_world<__nv_bfloat16, false>(c, slot, out, npacks, twoshot, blocks, stream);
+    return tree ? dispatch_world<__half, true>(c, slot, out, npacks, twoshot, blocks, threads, stream)
+                : dispatch_world<__half, false>(c, slot, out, npacks, twoshot, blocks, threads, stream);
+  return tree ? dispatch_world<__nv_bfloat16, true>(c, slot, out, npacks, twoshot, blocks, threads, stream)
+              : dispatch_world<__nv_bfloat16, false>(c, slot, out, npacks, twoshot, blocks, threads, stream);
 }
 
 int ar_gemm_tree_allreduce(tbik_ar_t h, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
@@ -365,6 +368,11 @@ int ar_configure(tbik_ar_t h, int key, int64_t value) {
     case TBIK_AR_CFG_ONESHOT_MAX_BYTES: c->oneshot_max_bytes = static_cast<size_t>(value); return TBIK_OK;
     case TBIK_AR_CFG_MAX_BLOCKS: c->max_blocks = static_cast<int>(value); return TBIK_OK;
     case TBIK_AR_CFG_WAIT_LIMIT_NS: c->wait_limit_ns = static_cast<uint64_t>(value); return TBIK_OK;
+    case TBIK_AR_CFG_THREADS:
+      if (value != 0 && (value < 32 || value > kThreads || value % 32 != 0))
+        return set_error(TBIK_ERR_ARG, "tbik_ar_configure: threads must be a multiple of 32 in [32, 512]");
+      c->threads = static_cast<int>(value);
+      return TBIK_OK;
     default: return set_error(TBIK_ERR_ARG, "tbik_ar_configure: unknown key");
   }
 }

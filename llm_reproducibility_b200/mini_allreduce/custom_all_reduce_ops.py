@@ -62,7 +62,7 @@ def tree_matmul_allreduce(fa: int, A: torch.Tensor, B: torch.Tensor, reg_buffer:
 
 
 # keys of `configure`
-CFG_SCRATCH_BYTES, CFG_ONESHOT_MAX_BYTES, CFG_MAX_BLOCKS, CFG_WAIT_LIMIT_NS = 1, 2, 3, 4
+CFG_SCRATCH_BYTES, CFG_ONESHOT_MAX_BYTES, CFG_MAX_BLOCKS, CFG_WAIT_LIMIT_NS, CFG_THREADS = 1, 2, 3, 4, 5
 
 
 def configure(fa: int, key: int, value: int) -> None:

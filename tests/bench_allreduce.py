@@ -2,7 +2,10 @@
 against NCCL all_reduce and the all_gather + ordered-adds path, bf16, 8 KB ... 64 MB, one process per GPU.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
-        tests/bench_allreduce.py [--iters 20] [--warmup 5] [--max-mb 64]
+        tests/bench_allreduce.py [--iters 20] [--warmup 5] [--max-mb 64] [--min-kb 8]
+                                 [--oneshot-max-kb K] [--max-blocks B] [--threads T] [--only-p2p]
+
+--oneshot-max-kb / --max-blocks override the built-in schedule choice (for tuning sweeps).
 
 Counterpart of the reference's tests/bench_allreduce.py:19-135, with device timing (CUDA events, max
 over ranks) instead of wall clock and without the clone inside the timed region.
@@ -25,6 +28,11 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--max-mb", type=int, default=64)
+    ap.add_argument("--min-kb", type=int, default=8)
+    ap.add_argument("--oneshot-max-kb", type=int, default=0)
+    ap.add_argument("--max-blocks", type=int, default=0)
+    ap.add_argument("--threads", type=int, default=0)
+    ap.add_argument("--only-p2p", action="store_true")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -37,6 +45,13 @@ def main():
     max_bytes = args.max_mb << 20
     ar = CustomTreeAllreduce(group=dist.group.WORLD, device=dev, max_size=max_bytes + (1 << 20))
     assert not ar.disabled
+    from llm_reproducibility_b200.mini_allreduce import custom_all_reduce_ops as ops
+    if args.oneshot_max_kb:
+        ops.configure(ar._ptr, ops.CFG_ONESHOT_MAX_BYTES, args.oneshot_max_kb << 10)
+    if args.threads:
+        ops.configure(ar._ptr, ops.CFG_THREADS, args.threads)
+    if args.max_blocks:
+        ops.configure(ar._ptr, ops.CFG_MAX_BLOCKS, args.max_blocks)
 
     def timed(fn):
         for _ in range(args.warmup):
@@ -54,7 +69,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()) * 1e3  # us
 
-    nbytes = 8192
+    nbytes = args.min_kb << 10
     while nbytes <= max_bytes:
         numel = nbytes // 2
         g = torch.Generator(device=dev).manual_seed(1000 + rank)
@@ -67,9 +82,10 @@ def main():
             "bytes": nbytes, "world": world,
             "tree_p2p_staged_us": timed(lambda: ar.all_reduce(x, out=out)),
             "tree_p2p_registered_us": timed(lambda: ar.all_reduce(view, out=out, registered=True)),
-            "nccl_allreduce_us": timed(lambda: dist.all_reduce(nccl_buf)),
-            "allgather_adds_us": timed(lambda: tree_all_reduce_sum_native(x, None)),
         }
+        if not args.only_p2p:
+            res["nccl_allreduce_us"] = timed(lambda: dist.all_reduce(nccl_buf))
+            res["allgather_adds_us"] = timed(lambda: tree_all_reduce_sum_native(x, None))
         t = res["tree_p2p_registered_us"] * 1e-6
         res["algbw_GBs"] = nbytes / t / 1e9
         res["busbw_GBs"] = nbytes * 2 * (world - 1) / world / t / 1e9
