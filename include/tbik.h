@@ -78,9 +78,25 @@ size_t tbik_gemm_workspace_bytes(int M, int N, int64_t K, int leaf);
 int tbik_gemm_ws(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
                  int dtype, int leaf, int node_dtype, void* workspace, size_t workspace_bytes, tbik_stream_t stream);
 
+/* K-slabs.  When C has too few tiles to give every SM one (decode-sized M), tbik_gemm_ws cuts K into 2, 4, 8 or 16
+ * slabs, each a whole subtree of the reduction tree, runs every (tile, slab) pair as its own work item, lets slab s
+ * store its subtree root in the workspace and finishes the tree with a small second kernel that adds the roots
+ * pairwise in the element type.  That is the arithmetic the reference applies across tensor-parallel ranks
+ * (per-rank tree of K / tp, then the rank-pair tree: src/tbik/tree_based_matmul.py:240-249 with
+ * mini_allreduce/tbik_kernel/csrc/allreduce/custom_all_reduce.cuh:203-234), applied inside one GPU, so the bits do
+ * not change.  tbik_gemm_workspace_bytes includes the room for the roots.  tbik_gemm_slabs runs one explicit
+ * (tiling 1..6, slabs = power of two <= min(16, T / F)) combination so that tests can prove the invariance;
+ * tbik_gemm_slabs_workspace_bytes gives its scratch need (0 for an invalid combination or when none is needed).
+ * The functions themselves have no counterpart in the reference. */
+size_t tbik_gemm_slabs_workspace_bytes(int M, int N, int64_t K, int leaf, int tiling, int slabs);
+int tbik_gemm_slabs(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
+                    int dtype, int leaf, int node_dtype, int tiling, int slabs, void* workspace, size_t workspace_bytes,
+                    tbik_stream_t stream);
+
 /* As tbik_gemm_ws, with the schedule exposed: at most `max_ctas` CTAs (0 = one per SM) and
  * `tiling` 0 = automatic, 1 = 128x128 tile per CTA, 2 = 256x128 per CTA pair, 3 = 128x256 per CTA,
- * 4 = 256x256 per CTA pair, 5 = 128x64 per CTA, 6 = 128x32 per CTA.  The result does not depend on either; the entry point exists so that
+ * 4 = 256x256 per CTA pair, 5 = 128x64 per CTA, 6 = 128x32 per CTA (an explicit tiling runs without K-slabs).
+ * The result does not depend on either; the entry point exists so that
  * tests can prove that. */
 int tbik_gemm_ex(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
                  int dtype, int leaf, int node_dtype, int max_ctas, int tiling, void* workspace,

@@ -28,6 +28,8 @@ _PROTOTYPES = {
     "tbik_gemm_workspace_bytes": (_sz, [_i32, _i32, _i64, _i32]),
     "tbik_gemm_ws": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _vp, _sz, _vp]),
     "tbik_gemm_ex": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
+    "tbik_gemm_slabs_workspace_bytes": (_sz, [_i32, _i32, _i64, _i32, _i32, _i32]),
+    "tbik_gemm_slabs": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "tbik_gemm_static": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
     "tbik_gemm_static_scratch_bytes": (_sz, []),
     "tbik_gemm_status": (_i32, [ctypes.POINTER(ctypes.c_uint32)]),

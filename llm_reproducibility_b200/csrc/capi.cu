@@ -36,7 +36,7 @@ int tbik_tree_shape(int64_t K, int leaf, int* T, int* F, int* L) {
 int tbik_gemm(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
               int dtype, int leaf, int node_dtype, tbik_stream_t stream) {
   return tbik::gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, 0, 0, nullptr, 0,
-                           static_cast<cudaStream_t>(stream));
+                           static_cast<cudaStream_t>(stream), 1);
 }
 
 size_t tbik_gemm_workspace_bytes(int M, int N, int64_t K, int leaf) { return tbik::gemm_workspace_bytes(M, N, K, leaf); }
@@ -44,14 +44,27 @@ size_t tbik_gemm_workspace_bytes(int M, int N, int64_t K, int leaf) { return tbi
 int tbik_gemm_ws(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
                  int dtype, int leaf, int node_dtype, void* workspace, size_t workspace_bytes, tbik_stream_t stream) {
   return tbik::gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, 0, 0, workspace, workspace_bytes,
-                           static_cast<cudaStream_t>(stream));
+                           static_cast<cudaStream_t>(stream), 0);
 }
 
 int tbik_gemm_ex(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
                  int dtype, int leaf, int node_dtype, int max_ctas, int tiling, void* workspace, size_t workspace_bytes,
                  tbik_stream_t stream) {
   return tbik::gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, max_ctas, tiling, workspace,
-                           workspace_bytes, static_cast<cudaStream_t>(stream));
+                           workspace_bytes, static_cast<cudaStream_t>(stream), tiling == 0 ? 0 : 1);
+}
+
+size_t tbik_gemm_slabs_workspace_bytes(int M, int N, int64_t K, int leaf, int tiling, int slabs) {
+  return tbik::gemm_split_workspace_bytes(M, N, K, leaf, tiling, slabs);
+}
+
+int tbik_gemm_slabs(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
+                    int dtype, int leaf, int node_dtype, int tiling, int slabs, void* workspace, size_t workspace_bytes,
+                    tbik_stream_t stream) {
+  if (tiling < 1) return tbik::set_error(TBIK_ERR_ARG, "tbik_gemm_slabs: an explicit tiling (1..6) is required");
+  if (slabs < 1) return tbik::set_error(TBIK_ERR_ARG, "tbik_gemm_slabs: slabs must be >= 1");
+  return tbik::gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, 0, tiling, workspace,
+                           workspace_bytes, static_cast<cudaStream_t>(stream), slabs);
 }
 
 size_t tbik_gemm_static_scratch_bytes(void) { return tbik::gemm_static_scratch_bytes(); }

@@ -15,8 +15,9 @@ int set_cuda_error(cudaError_t e, const char* what);
 int tree_shape(int64_t K, int leaf, int* T, int* F, int* L);
 int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
                 int dtype, int leaf, int node_dtype, int max_ctas, int tiling, void* workspace, size_t ws_bytes,
-                cudaStream_t stream);
+                cudaStream_t stream, int splits);  // splits: 0 = automatic (tiling 0 only), 1 = none, 2..16 = K-slabs
 size_t gemm_workspace_bytes(int M, int N, int64_t K, int leaf);
+size_t gemm_split_workspace_bytes(int M, int N, int64_t K, int leaf, int tiling, int splits);
 size_t gemm_static_scratch_bytes();
 
 // What the GEMM kernel needs from a communicator to reduce its own output tiles over peer memory.

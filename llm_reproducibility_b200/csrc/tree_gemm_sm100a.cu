@@ -78,6 +78,8 @@ struct GemmParams {
   int scratch_levels;    // levels per CTA held in `scratch`
   FusedDev f;            // used by the FUSED instantiation only
   int tma_store;         // 1: write C with TMA stores staged in the shared-memory stack slot (tmap_c valid)
+  int splits;            // K-slabs per output tile (power of two); slab s covers leaves [s*T, (s+1)*T) and writes
+  int64_t split_stride;  // its subtree root to C + s * split_stride elements (C = the partial buffer when > 1)
   uint32_t* status;      // [0] error code, [1] block, [2] role, [3] SM cycles of block 0 (last launch)
 };
 
@@ -332,7 +334,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_tiles = p.tiles_m * p.tiles_n * p.splits;  // work items: (output tile, K-slab)
   // scheduling unit: a CTA, or a pair of CTAs (cluster of 2) working on one 256-row tile
   static_assert(!(FUSED && PAIR), "the fused variant is single-CTA");
   const int gemm_ctas = FUSED ? static_cast<int>(gridDim.x) - p.f.comm_ctas : static_cast<int>(gridDim.x);
@@ -400,7 +402,8 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool ok = true;
       for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
         int tm, tn;
-        tile_coords(p, tile, tm, tn);
+        tile_coords(p, tile / p.splits, tm, tn);
+        const int kb0 = (tile % p.splits) * kblocks;                                       // first k-block of the slab
         const int row0 = tm * TILE_M + static_cast<int>(cta_rank) * BM;                   // this CTA's rows of A
         const int wrow0 = tn * BN + (PAIR ? static_cast<int>(cta_rank) * C_::B_ROWS : 0);  // its rows of W
         for (int kb = 0; kb < kblocks; ++kb) {
@@ -412,8 +415,8 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           // every CTA tracks its own bytes on its own barrier
           mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
-          tma_load_2d(sa, &tmap_a, kb * BK, row0, full_bar(stage));
-          tma_load_2d(sa + A_STAGE_BYTES, &tmap_b, kb * BK, wrow0, full_bar(stage));
+          tma_load_2d(sa, &tmap_a, (kb0 + kb) * BK, row0, full_bar(stage));
+          tma_load_2d(sa + A_STAGE_BYTES, &tmap_b, (kb0 + kb) * BK, wrow0, full_bar(stage));
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -625,9 +628,9 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t leaf_ctr = 0;
     for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
       int tm, tn;
-      tile_coords(p, tile, tm, tn);
+      tile_coords(p, tile / p.splits, tm, tn);
       const int row = tm * TILE_M + static_cast<int>(cta_rank) * BM + q * 32 + lane;
-      T* crow = reinterpret_cast<T*>(p.C) + static_cast<int64_t>(row) * p.ldc;
+      T* crow = reinterpret_cast<T*>(p.C) + (tile % p.splits) * p.split_stride + static_cast<int64_t>(row) * p.ldc;
       int c0 = 0;       // leaves already summed into the open level-0 group
       uint32_t g = 0;   // finished level-0 groups of this tile
       for (int leaf = 0; ok && leaf < p.T; ++leaf, ++leaf_ctr) {
@@ -748,6 +751,44 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (warp == 2) {
     tc_fence_after_sync();
     if constexpr (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS); else tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ K-slab combine
+// When a call has too few output tiles to give every SM one, K is cut into S slabs (S a power of two, each slab a
+// whole subtree of the reduction tree), every (tile, slab) pair becomes a work item of the GEMM kernel above, and
+// slab s writes its subtree root to part[s].  This kernel finishes the tree: out = the pairwise sum
+// ((p0+p1)+(p2+p3))+... of the roots, every add rounded to the element type -- the same upper tree levels one CTA
+// would have climbed, and the same arithmetic the rank-pair tree all-reduce applies to tensor-parallel shards.
+constexpr int kMaxSplits = 16;
+
+template <typename T, int S>
+__global__ void __launch_bounds__(256)
+slab_combine_kernel(const uint4* __restrict__ part, int64_t slab_packs, T* __restrict__ out, int M, int N, int64_t ldc,
+                    int ldp_packs, bool vec_ok) {
+  const int64_t total = static_cast<int64_t>(M) * ldp_packs;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    uint4 v[S];
+#pragma unroll
+    for (int k = 0; k < S; ++k) v[k] = part[k * slab_packs + i];
+#pragma unroll
+    for (int stride = 1; stride < S; stride *= 2) {
+#pragma unroll
+      for (int k = 0; k + stride < S; k += 2 * stride) v[k] = Elem<T>::add(v[k], v[k + stride]);
+    }
+    const int row = static_cast<int>(i / ldp_packs);
+    const int col0 = static_cast<int>(i % ldp_packs) * 8;
+    T* dst = out + static_cast<int64_t>(row) * ldc + col0;
+    if (vec_ok && col0 + 8 <= N) {
+      *reinterpret_cast<uint4*>(dst) = v[0];
+    } else {
+      const uint32_t w[4] = {v[0].x, v[0].y, v[0].z, v[0].w};
+      uint16_t* d16 = reinterpret_cast<uint16_t*>(dst);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (col0 + j < N) d16[j] = static_cast<uint16_t>(j & 1 ? w[j >> 1] >> 16 : w[j >> 1] & 0xFFFFu);
+    }
   }
 }
 
@@ -907,24 +948,39 @@ int tree_shape(int64_t K, int leaf, int* T, int* F, int* L) {
 
 // Schedule for one call: which variant, how many CTAs, how much scratch.
 struct Plan {
-  int tiling;  // 1..4
+  int tiling;  // 1..6
   bool deep;
   int grid;
   int tiles_m, tiles_n;
+  int splits;             // K-slabs per output tile (1 = the whole tree in one CTA)
+  int slab_levels;        // tree levels one work item climbs: L - log2(splits)
   int scratch_levels;
-  size_t scratch_bytes;
+  size_t scratch_bytes;   // global stack levels
+  size_t partial_off;     // offset of the slab roots in the workspace (0 when splits == 1)
+  size_t partial_bytes;   // [splits][M][N rounded up to 8] elements
+  size_t total_bytes() const { return splits > 1 ? partial_off + partial_bytes : scratch_bytes; }
 };
 
-static Plan make_plan(int tiling, int M, int N, int L, int max_ctas) {
+static int log2_int(int v) {
+  int l = 0;
+  while ((1 << l) < v) ++l;
+  return l;
+}
+
+// `L` is the depth of the whole tree; with `splits` > 1 each work item climbs only the lower L - log2(splits) levels.
+static Plan make_plan(int tiling, int M, int N, int L, int max_ctas, int splits = 1) {
   Plan pl{};
   pl.tiling = tiling;
+  pl.splits = splits;
+  L -= log2_int(splits);
+  pl.slab_levels = L;
   const Variant& shallow = kVariants[tiling - 1][0];
   pl.deep = (L - 1) > shallow.levels_on_chip;
   const Variant& v = kVariants[tiling - 1][pl.deep ? 1 : 0];
   const int tile_m = v.pair ? 2 * BM : BM;
   pl.tiles_m = (M + tile_m - 1) / tile_m;
   pl.tiles_n = (N + v.bn - 1) / v.bn;
-  const int num_tiles = pl.tiles_m * pl.tiles_n;
+  const int num_tiles = pl.tiles_m * pl.tiles_n * splits;
   int ctas = sm_count();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   int units = v.pair ? ctas / 2 : ctas;
@@ -933,13 +989,33 @@ static Plan make_plan(int tiling, int M, int N, int L, int max_ctas) {
   pl.grid = v.pair ? 2 * units : units;
   pl.scratch_levels = (L - 1) > v.levels_on_chip ? (L - 1) - v.levels_on_chip : 0;
   pl.scratch_bytes = static_cast<size_t>(pl.grid) * pl.scratch_levels * v.level_bytes;
+  if (splits > 1) {
+    pl.partial_off = (pl.scratch_bytes + 255) & ~size_t(255);
+    pl.partial_bytes = static_cast<size_t>(splits) * M * ((N + 7) / 8 * 8) * 2;
+  }
   return pl;
+}
+
+// Rough time of a plan in microseconds, from measurements at few rows of C: a CTA advances one 64-wide k-block every
+// 0.30 us (0.47 us for 256-column tiles) whatever the tile width, so what counts is the k-blocks per CTA.
+static double plan_cost_us(const Plan& pl, int M, int N, int kblocks_total, int ctas) {
+  const Variant& v = kVariants[pl.tiling - 1][pl.deep ? 1 : 0];
+  const int items = pl.tiles_m * pl.tiles_n * pl.splits;
+  const int units = v.pair ? ctas / 2 : ctas;
+  const int waves = (items + units - 1) / (units > 0 ? units : 1);
+  double t = 4.0 + waves * (kblocks_total / pl.splits) * (v.bn >= 256 ? 0.47 : 0.30);
+  if (pl.splits > 1) t += 2.5 + static_cast<double>(pl.splits + 1) * M * N * 2 / 3.0e6;  // combine launch + its bytes at 3 TB/s
+  return t;
 }
 
 // Automatic choice: the widest tile that still gives (nearly) every SM a tile -- wide tiles run the tensor
 // pipe faster, but with few rows of C the GEMM streams W from HBM and needs all SMs pulling.  128x256 needs
 // the caller's scratch for the upper tree levels; without it the 128-wide and narrower tilings are used.
-static Plan auto_plan(int M, int N, int L, int max_ctas, size_t ws_bytes, bool have_ws) {
+//
+// When even the narrowest tiling leaves SMs idle (decode-sized M), K is cut into slabs as well: every candidate
+// (tiling, slabs) that fits one wave and the caller's workspace is costed and the cheapest wins.  `groups` is the
+// number of level-0 groups of the tree (T / F), the finest cut that keeps every slab a whole subtree.
+static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int max_ctas, size_t ws_bytes, bool have_ws) {
   int ctas = sm_count();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   const int enough = ctas - ctas / 5;
@@ -949,25 +1025,74 @@ static Plan auto_plan(int M, int N, int L, int max_ctas, size_t ws_bytes, bool h
   for (int i = 0; i < 4; ++i) {
     Plan pl = make_plan(order[i], M, N, L, max_ctas);
     if (pl.scratch_bytes > 0 && !(have_ws && pl.scratch_bytes <= ws_bytes)) continue;
-    if (pl.tiles_m * pl.tiles_n >= enough) return pl;
+    if (pl.tiles_m * pl.tiles_n >= enough) {
+      if (order[i] == 3 || order[i] == 1 || !have_ws || groups < 2) return pl;  // enough rows of C: no slabs
+      best = pl;
+      have = true;
+      break;
+    }
     if (!have || pl.tiles_m * pl.tiles_n > best.tiles_m * best.tiles_n) {
       best = pl;
       have = true;
     }
   }
-  return have ? best : make_plan(1, M, N, L, max_ctas);
+  if (!have) best = make_plan(1, M, N, L, max_ctas);
+  if (!have_ws || groups < 2) return best;
+  double best_cost = plan_cost_us(best, M, N, kblocks_total, ctas);
+  for (int i = 0; i < 4; ++i) {
+    for (int s = 2; s <= kMaxSplits && s <= groups; s *= 2) {
+      Plan pl = make_plan(order[i], M, N, L, max_ctas, s);
+      if (pl.tiles_m * pl.tiles_n * s > ctas) break;  // one wave only
+      if (pl.total_bytes() > ws_bytes) continue;
+      const double c = plan_cost_us(pl, M, N, kblocks_total, ctas);
+      if (c < best_cost) {
+        best = pl;
+        best_cost = c;
+      }
+    }
+  }
+  return best;
 }
 
 size_t gemm_workspace_bytes(int M, int N, int64_t K, int leaf) {
   int T, F, L;
   if (M <= 0 || N <= 0 || tree_shape(K, leaf, &T, &F, &L) != TBIK_OK) return 0;
   // what the automatic choice would like to have if scratch were unlimited
-  return auto_plan(M, N, L, 0, ~size_t(0), true).scratch_bytes;
+  return auto_plan(M, N, L, T / F, T * (leaf / BK), 0, ~size_t(0), true).total_bytes();
+}
+
+size_t gemm_split_workspace_bytes(int M, int N, int64_t K, int leaf, int tiling, int splits) {
+  int T, F, L;
+  if (M <= 0 || N <= 0 || tree_shape(K, leaf, &T, &F, &L) != TBIK_OK) return 0;
+  if (tiling < 1 || tiling > 6 || splits < 1 || splits > kMaxSplits || (splits & (splits - 1)) || splits > T / F) return 0;
+  return make_plan(tiling, M, N, L, 0, splits).total_bytes();
+}
+
+template <typename T>
+static int launch_combine(int splits, const void* part, T* out, int M, int N, int64_t ldc, cudaStream_t stream) {
+  const int ldp_packs = (N + 7) / 8;
+  const int64_t slab_packs = static_cast<int64_t>(M) * ldp_packs;
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(out) & 15u) == 0 && ldc % 8 == 0;
+  int64_t blocks = (slab_packs + 255) / 256;
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  const uint4* p4 = static_cast<const uint4*>(part);
+  const int g = static_cast<int>(blocks);
+  switch (splits) {
+    case 2: slab_combine_kernel<T, 2><<<g, 256, 0, stream>>>(p4, slab_packs, out, M, N, ldc, ldp_packs, vec_ok); break;
+    case 4: slab_combine_kernel<T, 4><<<g, 256, 0, stream>>>(p4, slab_packs, out, M, N, ldc, ldp_packs, vec_ok); break;
+    case 8: slab_combine_kernel<T, 8><<<g, 256, 0, stream>>>(p4, slab_packs, out, M, N, ldc, ldp_packs, vec_ok); break;
+    case 16: slab_combine_kernel<T, 16><<<g, 256, 0, stream>>>(p4, slab_packs, out, M, N, ldc, ldp_packs, vec_ok); break;
+    default: return set_error(TBIK_ERR_ARG, "slab combine: unsupported slab count");
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_cuda_error(e, "slab combine kernel launch");
+  return TBIK_OK;
 }
 
 int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
                 int dtype, int leaf, int node_dtype, int max_ctas, int tiling, void* workspace, size_t ws_bytes,
-                cudaStream_t stream) {
+                cudaStream_t stream, int splits) {
   if (dtype != TBIK_DTYPE_BF16 && dtype != TBIK_DTYPE_FP16)
     return set_error(TBIK_ERR_DTYPE, "tbik_gemm supports bf16 and fp16 operands");
   if (node_dtype != TBIK_NODE_INPUT)
@@ -989,12 +1114,18 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
     return set_error(TBIK_ERR_ALIGN, "tbik_gemm: workspace must be 16-byte aligned");
   const bool have_ws = workspace != nullptr && ws_bytes > 0;
 
-  const Plan pl = tiling == 0 ? auto_plan(M, N, L, max_ctas, ws_bytes, have_ws) : make_plan(tiling, M, N, L, max_ctas);
-  if (pl.scratch_bytes > 0 && (!have_ws || pl.scratch_bytes > ws_bytes)) {
+  // splits: 0 = automatic (only together with tiling 0), 1 = none, else a power of two of whole subtrees
+  if (splits < 0 || splits > kMaxSplits || (splits & (splits - 1)) != 0)
+    return set_error(TBIK_ERR_ARG, "tbik_gemm: the number of K-slabs must be a power of two up to 16");
+  if (splits > 1 && (tiling == 0 || splits > T / F))
+    return set_error(TBIK_ERR_SHAPE, "tbik_gemm: K-slabs need an explicit tiling and at most T / F slabs (whole subtrees)");
+  const Plan pl = tiling == 0 ? auto_plan(M, N, L, splits == 1 ? 1 : T / F, T * (leaf / BK), max_ctas, ws_bytes, have_ws)
+                              : make_plan(tiling, M, N, L, max_ctas, splits > 1 ? splits : 1);
+  if (pl.total_bytes() > 0 && (!have_ws || pl.total_bytes() > ws_bytes)) {
     char msg[200];
     snprintf(msg, sizeof(msg),
              "tbik_gemm: a reduction tree of %d levels needs %zu bytes of scratch for this tiling (got %zu); "
-             "see tbik_gemm_workspace_bytes", L, pl.scratch_bytes, have_ws ? ws_bytes : size_t(0));
+             "see tbik_gemm_workspace_bytes", L, pl.total_bytes(), have_ws ? ws_bytes : size_t(0));
     return set_error(TBIK_ERR_SHAPE, msg);
   }
   const Variant& v = kVariants[pl.tiling - 1][pl.deep ? 1 : 0];
@@ -1011,9 +1142,11 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
   p.M = M;
   p.N = N;
   p.kblocks_per_leaf = leaf / BK;
-  p.T = T;
+  p.T = T / pl.splits;
   p.F = F;
-  p.L = L;
+  p.L = pl.slab_levels;
+  p.splits = pl.splits;
+  p.split_stride = 0;
   p.tiles_m = pl.tiles_m;
   p.tiles_n = pl.tiles_n;
   p.group_m = v.pair ? 8 : 16;  // 2048 rows of A per group: a wave of CTAs covers a near-square block of C
@@ -1027,12 +1160,23 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
   // epilogue threads store their rows directly.
   CUtensorMap tc{};
   p.tma_store = 0;
-  if ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && ldc % 8 == 0 &&
-      make_tmap(&tc, dtype, C, M, N, ldc, BM, true) == TBIK_OK)
+  if (pl.splits > 1) {
+    // slab roots go to the workspace with direct stores; the combine kernel writes C
+    const int64_t ldp = (N + 7) / 8 * 8;
+    p.C = static_cast<unsigned char*>(workspace) + pl.partial_off;
+    p.ldc = ldp;
+    p.split_stride = static_cast<int64_t>(M) * ldp;
+  } else if ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && ldc % 8 == 0 &&
+             make_tmap(&tc, dtype, C, M, N, ldc, BM, true) == TBIK_OK) {
     p.tma_store = 1;
+  }
 
-  if (dtype == TBIK_DTYPE_BF16) return launch_variant<__nv_bfloat16>(pl.tiling, pl.deep, ta, tb, tc, p, pl.grid, stream);
-  return launch_variant<__half>(pl.tiling, pl.deep, ta, tb, tc, p, pl.grid, stream);
+  rc = dtype == TBIK_DTYPE_BF16 ? launch_variant<__nv_bfloat16>(pl.tiling, pl.deep, ta, tb, tc, p, pl.grid, stream)
+                                : launch_variant<__half>(pl.tiling, pl.deep, ta, tb, tc, p, pl.grid, stream);
+  if (rc != TBIK_OK || pl.splits == 1) return rc;
+  if (dtype == TBIK_DTYPE_BF16)
+    return launch_combine<__nv_bfloat16>(pl.splits, p.C, static_cast<__nv_bfloat16*>(C), M, N, ldc, stream);
+  return launch_combine<__half>(pl.splits, p.C, static_cast<__half*>(C), M, N, ldc, stream);
 }
 
 // ---------------------------------------------------------------- GEMM + tree all-reduce in one launch
@@ -1081,6 +1225,7 @@ int gemm_launch_fused(const void* A, const void* W, void* part, int M, int N, in
   p.tiles_m = pl.tiles_m;
   p.tiles_n = pl.tiles_n;
   p.group_m = 16;
+  p.splits = 1;
   p.scratch = static_cast<uint32_t*>(workspace);
   p.scratch_levels = pl.scratch_levels;
   p.tma_store = 1;
@@ -1146,7 +1291,7 @@ int gemm_launch_static(const void* A, const void* W, void* C, int M, int N, int 
     return set_error(TBIK_ERR_SHAPE, msg);
   }
   return gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, 0, 0, device_addr[dev],
-                     kStaticScratchBytes, stream);
+                     kStaticScratchBytes, stream, 0);
 }
 
 int gemm_status(uint32_t out[4]) {

@@ -109,7 +109,8 @@ def test_entry_point_without_scratch_matches_the_one_with_scratch():
     L = _lib.lib()
     M, K, N = 1000, 12288, 4096
     assert L.tbik_gemm_workspace_bytes(M, N, K, 256) > 0          # 128x256 tiles, 5-level tree: 3 levels go to scratch
-    assert L.tbik_gemm_workspace_bytes(64, N, K, 256) == 0        # small M: no scratch needed
+    assert L.tbik_gemm_workspace_bytes(64, N, K, 256) > 0         # small M: room for the K-slab roots
+    assert L.tbik_gemm_workspace_bytes(64, N, 256, 256) == 0      # one leaf: nothing to cut, no scratch
     g = torch.Generator(device="cuda").manual_seed(1)
     A = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
     W = (torch.randn(N, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
@@ -215,6 +216,74 @@ def test_result_does_not_depend_on_cta_count(tiling):
     outs = [_gemm_ex(Ad, W, 700, 520, 1536, ctas, tiling) for ctas in (0, 1, 2, 3, 7, 148)]
     for C in outs[1:]:
         assert torch.equal(bits(C), bits(outs[0]))
+
+
+def _gemm_slabs(Ad, W, M, N, K, tiling, slabs, dtype_code=0, leaf=256, ldc=None):
+    from llm_reproducibility_b200 import _lib
+    L = _lib.lib()
+    ldc = ldc or N
+    C = torch.zeros(M, ldc, dtype=Ad.dtype, device="cuda")
+    need = L.tbik_gemm_slabs_workspace_bytes(M, N, K, leaf, tiling, slabs)
+    assert need > 0 or slabs == 1
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    rc = L.tbik_gemm_slabs(Ad.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K, K, K, ldc, dtype_code, leaf, _lib.NODE_INPUT,
+                           tiling, slabs, ws.data_ptr(), need, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    from llm_reproducibility_b200.tbik.tree_based_matmul import gemm_device_status
+    assert gemm_device_status()[0] == 0
+    return C[:, :N]
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 4096), (16, 12288, 4096), (128, 12288, 520), (200, 2048, 1000),
+                                   (64, 1536, 4096), (300, 8192, 264), (7, 6144, 99)])
+def test_k_slabs_give_the_same_bits(M, K, N):
+    """Cutting K into 2..16 subtrees that separate CTAs compute, then adding the roots pairwise, is the reduction tree
+    itself: every (tiling, slabs) combination equals the unsplit kernel bit for bit (random operands) and the oracle
+    (integer operands).  N not a multiple of 8 and a padded C exercise the scalar stores of the combine kernel."""
+    from llm_reproducibility_b200 import _lib
+    T, F, _ = (ctypes.c_int(), ctypes.c_int(), ctypes.c_int())
+    assert _lib.lib().tbik_tree_shape(K, 256, ctypes.byref(T), ctypes.byref(F), ctypes.byref(_)) == 0
+    groups = T.value // F.value
+    g = torch.Generator(device="cuda").manual_seed(M * 3 + K + N)
+    A = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    W = (torch.randn(N, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    one = _gemm_ex(A, W, M, N, K, 0, 1)
+    Ai, Bi = exact_int_inputs(M, K, N, torch.bfloat16, seed=K + N, amax=7)
+    ref_i = tbik_matmul_ref(Ai, Bi)
+    Aid, Wi = Ai.cuda(), Bi.cuda().t().contiguous()
+    tested = 0
+    for tiling in TILINGS:
+        for slabs in (2, 4, 8, 16):
+            if slabs > groups:
+                assert _lib.lib().tbik_gemm_slabs_workspace_bytes(M, N, K, 256, tiling, slabs) == 0
+                continue
+            assert torch.equal(bits(_gemm_slabs(A, W, M, N, K, tiling, slabs)), bits(one)), (tiling, slabs)
+            assert torch.equal(bits(_gemm_slabs(Aid, Wi, M, N, K, tiling, slabs, ldc=N + 24).cpu()), bits(ref_i)), (tiling, slabs)
+            tested += 1
+    assert tested >= 6
+    h, Wh = A.to(torch.float16), W.to(torch.float16)
+    one = _gemm_ex(h, Wh, M, N, K, 0, 1, dtype_code=1)
+    assert torch.equal(bits(_gemm_slabs(h, Wh, M, N, K, 3, 2, dtype_code=1)), bits(one))
+
+
+def test_k_slab_argument_errors():
+    from llm_reproducibility_b200 import _lib
+    L = _lib.lib()
+    A = torch.zeros(16, 1024, dtype=torch.bfloat16, device="cuda")
+    W = torch.zeros(64, 1024, dtype=torch.bfloat16, device="cuda")
+    C = torch.zeros(16, 64, dtype=torch.bfloat16, device="cuda")
+    ws = torch.empty(1 << 20, dtype=torch.uint8, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    call = lambda tiling, slabs, wsb: L.tbik_gemm_slabs(A.data_ptr(), W.data_ptr(), C.data_ptr(), 16, 64, 1024, 1024, 1024, 64,
+                                                        0, 256, 0, tiling, slabs, ws.data_ptr(), wsb, s)
+    assert call(0, 2, ws.numel()) == -1                       # automatic tiling is not accepted here
+    assert call(1, 3, ws.numel()) == -1                       # not a power of two
+    assert call(1, 32, ws.numel()) == -1                      # more than 16
+    assert call(1, 4, ws.numel()) == -2 and "subtrees" in _lib.last_error()   # T = 4, F = 2: only 2 whole subtrees
+    assert call(1, 2, 64) == -2 and "scratch" in _lib.last_error()            # workspace too small for the roots
+    assert call(1, 2, ws.numel()) == 0
+    torch.cuda.synchronize()
 
 
 @pytest.mark.parametrize("M,K,N", [(1, 4096, 512), (100, 4096, 512), (128, 12288, 256), (129, 4096, 384),
