@@ -395,7 +395,9 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (every CTA)
-    if (lane == 0) {
+    // elect.sync, not lane == 0: the compiler then knows that one thread runs the branch and feeds the TMA
+    // and UMMA instructions from uniform registers directly, instead of looping over the active lanes
+    if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
       const int kblocks = p.T * p.kblocks_per_leaf;
@@ -433,7 +435,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp == 1) {
     if (PAIR && !leader) {
       // ---------------------------------------------------------- partner CTA: relay "stage landed" to the leader
-      if (lane == 0) {
+      if (elect_one()) {
         int stage = 0;
         uint32_t phase = 0;
         const int kblocks = p.T * p.kblocks_per_leaf;
@@ -453,7 +455,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
       }
-    } else if (lane == 0) {
+    } else if (elect_one()) {
       // ---------------------------------------------------------- UMMA issuer (pair: leader CTA only)
       constexpr uint32_t IDESC = umma_idesc_f16(Pack16<T>::kUmmaFmt, TILE_M, BN);
       const uint64_t desc_a0 = umma_desc_sw128_kmajor(smem_base);
@@ -581,7 +583,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     auto epi_sync = [&]() {
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_base + C_::OFF_EPI_BAR);
-      if (!mbar_wait_bounded(smem_base + C_::OFF_EPI_BAR, epi_phase, abort_flag, WAIT_LIMIT_NS)) {
+      if (!mbar_wait_bounded_warp(smem_base + C_::OFF_EPI_BAR, epi_phase, abort_flag, WAIT_LIMIT_NS)) {
         ok = false;
         role_failed = 6;
       }
@@ -614,7 +616,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
         for (int leaf = 0; ok && leaf < p.T; ++leaf, ++ctr) {
           const uint32_t a = ctr & 1u;
-          if (!mbar_wait_bounded(tfull_bar(a), (ctr >> 1) & 1u, abort_flag, WAIT_LIMIT_NS)) {
+          if (!mbar_wait_bounded_warp(tfull_bar(a), (ctr >> 1) & 1u, abort_flag, WAIT_LIMIT_NS)) {
             ok = false;
             role_failed = 4;
             break;
@@ -636,7 +638,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int leaf = 0; ok && leaf < p.T; ++leaf, ++leaf_ctr) {
         const uint32_t a = leaf_ctr & 1u;
         const uint32_t aphase = (leaf_ctr >> 1) & 1u;
-        if (!mbar_wait_bounded(tfull_bar(a), aphase, abort_flag, WAIT_LIMIT_NS)) {
+        if (!mbar_wait_bounded_warp(tfull_bar(a), aphase, abort_flag, WAIT_LIMIT_NS)) {
           ok = false;
           role_failed = 4;
           break;
