@@ -80,6 +80,23 @@ TBIK_DEVICE bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait that lets the hardware park the thread for up to `ns` while the phase is open (it is woken when
+// the phase completes).  A waiting warp that polls instead takes issue slots from the warps of its
+// scheduler partition, among them the single threads that feed the TMA unit and the tensor core.
+TBIK_DEVICE bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  Returns false when the wait gave up: either another thread of the CTA
 // raised `*abort_flag`, or `limit_ns` of wall time went by (then this thread raises it).
 // A false return means "stop working and go to the tear-down path".
@@ -88,7 +105,7 @@ TBIK_DEVICE bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile uint3
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
     if ((it & 63u) == 0u) {
       if (*abort_flag != 0u) return false;
       if (global_timer_ns() - t0 > limit_ns) {

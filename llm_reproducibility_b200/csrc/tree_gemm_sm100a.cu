@@ -408,11 +408,12 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int kb0 = (tile % p.splits) * kblocks;                                       // first k-block of the slab
         const int row0 = tm * TILE_M + static_cast<int>(cta_rank) * BM;                   // this CTA's rows of A
         const int wrow0 = tn * BN + (PAIR ? static_cast<int>(cta_rank) * C_::B_ROWS : 0);  // its rows of W
-        for (int kb = 0; kb < kblocks; ++kb) {
+        // one 64-wide k-block: wait for a free stage, arm its barrier, two tiled loads
+        auto load_kblock = [&](int kb) -> bool {
           if (!mbar_wait_bounded(empty_bar(stage), phase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
             ok = false;
             role_failed = 1;
-            break;
+            return false;
           }
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           // every CTA tracks its own bytes on its own barrier
@@ -422,6 +423,20 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
+          }
+          return true;
+        };
+        if ((kblocks & 3) == 0) {
+          // straight-line code for four k-blocks: a taken branch per k-block costs more than issuing its loads
+          for (int kb = 0; ok && kb < kblocks; kb += 4) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (!load_kblock(kb + u)) break;
+            }
+          }
+        } else {
+          for (int kb = 0; kb < kblocks; ++kb) {
+            if (!load_kblock(kb)) break;
           }
         }
       }
@@ -484,11 +499,12 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           tc_fence_after_sync();
           const uint32_t tmem_d = tmem_base + a * BN;
-          for (int kb = 0; kb < p.kblocks_per_leaf; ++kb) {
+          // one 64-wide k-block: wait for its stage, four UMMAs, release the stage
+          auto kblock = [&](int kb) -> bool {
             if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
               ok = false;
               role_failed = 3;
-              break;
+              return false;
             }
             tc_fence_after_sync();
             const uint64_t sd = static_cast<uint64_t>(stage) * (STAGE_BYTES >> 4);
@@ -504,6 +520,18 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (++stage == STAGES) {
               stage = 0;
               phase ^= 1u;
+            }
+            return true;
+          };
+          if (p.kblocks_per_leaf == 4) {
+            // the usual leaf of 256: straight-line code, a taken branch per k-block costs more than its UMMAs
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
+              if (!kblock(kb)) break;
+            }
+          } else {
+            for (int kb = 0; kb < p.kblocks_per_leaf; ++kb) {
+              if (!kblock(kb)) break;
             }
           }
           if (ok) commit(tfull_bar(a));
@@ -1010,9 +1038,10 @@ static double plan_cost_us(const Plan& pl, int M, int N, int kblocks_total, int 
   return t;
 }
 
-// Automatic choice: the widest tile that still gives (nearly) every SM a tile -- wide tiles run the tensor
-// pipe faster, but with few rows of C the GEMM streams W from HBM and needs all SMs pulling.  128x256 needs
-// the caller's scratch for the upper tree levels; without it the 128-wide and narrower tilings are used.
+// Automatic choice: the first tiling, in order of measured speed at large M (256x128 per CTA pair: operands
+// shared by two SMs, the whole tree stack in tensor memory, eight pipeline stages; then 128x256, 128x128),
+// that still gives (nearly) every SM a tile; with few rows of C the GEMM streams W from HBM and needs all SMs
+// pulling, so the narrow tilings follow.  128x256 needs the caller's scratch for the upper tree levels.
 //
 // When even the narrowest tiling leaves SMs idle (decode-sized M), K is cut into slabs as well: every candidate
 // (tiling, slabs) that fits one wave and the caller's workspace is costed and the cheapest wins.  `groups` is the
@@ -1021,14 +1050,15 @@ static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int ma
   int ctas = sm_count();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   const int enough = ctas - ctas / 5;
-  const int order[4] = {3, 1, 5, 6};
+  const int order[5] = {2, 3, 1, 5, 6};
   Plan best{};
   bool have = false;
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < 5; ++i) {
     Plan pl = make_plan(order[i], M, N, L, max_ctas);
     if (pl.scratch_bytes > 0 && !(have_ws && pl.scratch_bytes <= ws_bytes)) continue;
-    if (pl.tiles_m * pl.tiles_n >= enough) {
-      if (order[i] == 3 || order[i] == 1 || !have_ws || groups < 2) return pl;  // enough rows of C: no slabs
+    const Variant& pv = kVariants[order[i] - 1][pl.deep ? 1 : 0];
+    if (pl.tiles_m * pl.tiles_n * (pv.pair ? 2 : 1) >= enough) {
+      if (order[i] <= 3 || !have_ws || groups < 2) return pl;  // enough rows of C: no slabs
       best = pl;
       have = true;
       break;
@@ -1041,10 +1071,10 @@ static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int ma
   if (!have) best = make_plan(1, M, N, L, max_ctas);
   if (!have_ws || groups < 2) return best;
   double best_cost = plan_cost_us(best, M, N, kblocks_total, ctas);
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < 5; ++i) {
     for (int s = 2; s <= kMaxSplits && s <= groups; s *= 2) {
       Plan pl = make_plan(order[i], M, N, L, max_ctas, s);
-      if (pl.tiles_m * pl.tiles_n * s > ctas) break;  // one wave only
+      if (pl.tiles_m * pl.tiles_n * s * (kVariants[order[i] - 1][0].pair ? 2 : 1) > ctas) break;  // one wave only
       if (pl.total_bytes() > ws_bytes) continue;
       const double c = plan_cost_us(pl, M, N, kblocks_total, ctas);
       if (c < best_cost) {
@@ -1262,8 +1292,9 @@ size_t gemm_fused_workspace_bytes(int M, int N, int64_t K, int leaf) {
 
 // ---------------------------------------------------------------- the entry point that allocates nothing
 // Scratch for the upper stack levels, built into the library image: every GPU that loads the library
-// holds these bytes until the process exits.  32 MiB covers the 128x256 tiling of every Qwen3-8B
-// row-split layer (down_proj, 5 tree levels: 148 CTAs x 3 levels x 64 KiB = 27.75 MiB).
+// holds these bytes until the process exits.  32 MiB covers every schedule the automatic choice picks
+// for a Qwen3-8B row-split layer (the K-slab roots of a decode-sized call are under 10 MiB) and the
+// 128x256 tiling of its deepest tree (down_proj, 5 levels: 148 CTAs x 3 levels x 64 KiB = 27.75 MiB).
 constexpr size_t kStaticScratchBytes = size_t(32) << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 

@@ -102,24 +102,33 @@ def test_very_deep_tree_scratch_rules():
         assert torch.equal(bits(_gemm_ex(Ad, W, 130, 136, 65536, 0, tiling).cpu()), bits(ref)), tiling
 
 
-def test_entry_point_without_scratch_matches_the_one_with_scratch():
-    """tbik_gemm (no scratch, 128x128 tiles) and tbik_gemm_ws (128x256 tiles for M > 128) agree bitwise."""
+def test_entry_point_without_scratch_matches_the_ones_with_scratch():
+    """tbik_gemm (no scratch: the stack of the chosen tiling fits on chip), the 128x256 tiling (needs scratch for a
+    5-level tree) and tbik_gemm_ws at a decode-sized M (K-slabs, roots in the workspace) agree bitwise."""
     from llm_reproducibility_b200 import _lib
     from llm_reproducibility_b200.tbik.tree_based_matmul import matmul_tp_persistent
     L = _lib.lib()
     M, K, N = 1000, 12288, 4096
-    assert L.tbik_gemm_workspace_bytes(M, N, K, 256) > 0          # 128x256 tiles, 5-level tree: 3 levels go to scratch
+    assert L.tbik_gemm_workspace_bytes(M, N, K, 256) == 0         # 256x128 pair tiles: the whole stack in tensor memory
+    assert L.tbik_gemm_slabs_workspace_bytes(M, N, K, 256, 3, 1) > 0   # 128x256 tiles, 5-level tree: 3 levels go to scratch
     assert L.tbik_gemm_workspace_bytes(64, N, K, 256) > 0         # small M: room for the K-slab roots
     assert L.tbik_gemm_workspace_bytes(64, N, 256, 256) == 0      # one leaf: nothing to cut, no scratch
     g = torch.Generator(device="cuda").manual_seed(1)
     A = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
     W = (torch.randn(N, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
     C0 = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-    assert L.tbik_gemm(A.data_ptr(), W.data_ptr(), C0.data_ptr(), M, N, K, K, K, N, 0, 256, 0,
-                       torch.cuda.current_stream().cuda_stream) == 0
+    s = torch.cuda.current_stream().cuda_stream
+    assert L.tbik_gemm(A.data_ptr(), W.data_ptr(), C0.data_ptr(), M, N, K, K, K, N, 0, 256, 0, s) == 0
     C1 = matmul_tp_persistent(A, W.t())
+    C3 = _gemm_ex(A, W, M, N, K, 0, 3)
     torch.cuda.synchronize()
-    assert torch.equal(bits(C0), bits(C1))
+    assert torch.equal(bits(C0), bits(C1)) and torch.equal(bits(C0), bits(C3))
+    # decode-sized M: no scratch -> one CTA per tile, with scratch -> K-slabs; same bits
+    C4 = torch.empty(64, N, dtype=torch.bfloat16, device="cuda")
+    assert L.tbik_gemm(A.data_ptr(), W.data_ptr(), C4.data_ptr(), 64, N, K, K, K, N, 0, 256, 0, s) == 0
+    C5 = matmul_tp_persistent(A[:64], W.t())
+    torch.cuda.synchronize()
+    assert torch.equal(bits(C4), bits(C5)) and torch.equal(bits(C4), bits(C0[:64]))
 
 
 @pytest.mark.parametrize("leaf,K", [(128, 3200), (64, 1600), (640, 3200), (512, 4096)])

@@ -33,10 +33,13 @@ def _run(fn, A, W, extra=()):
     return C
 
 
-def test_static_scratch_entry_point_matches_workspace_entry_point_twice():
+@pytest.mark.parametrize("M,K,N", [
+    (64, 12288, 4096),     # decode-sized: K-slabs, the slab roots live in the scratch
+    (300, 65536, 1024),    # 8-level tree: one stack level beyond tensor memory and shared memory goes to scratch
+])
+def test_static_scratch_entry_point_matches_workspace_entry_point_twice(M, K, N):
     from llm_reproducibility_b200 import _lib
     L = _lib.lib()
-    M, K, N = 1000, 12288, 4096           # 5-level tree: the 128x256 tiling keeps 3 levels in scratch
     need = L.tbik_gemm_workspace_bytes(M, N, K, 256)
     assert 0 < need <= L.tbik_gemm_static_scratch_bytes()
     ws = torch.empty(need, dtype=torch.uint8, device="cuda")
@@ -54,7 +57,7 @@ def test_static_scratch_entry_point_matches_workspace_entry_point_twice():
 def test_static_scratch_entry_point_refuses_sizes_beyond_its_array():
     from llm_reproducibility_b200 import _lib
     L = _lib.lib()
-    M, K, N = 8192, 65536, 4096           # 8-level tree on 148 CTAs: 6 levels x 64 KiB x 148 > 32 MiB
+    M, K, N = 8192, 1 << 23, 4096         # 15-level tree: 8 stack levels x 32 KiB x 148 CTAs > 32 MiB
     assert L.tbik_gemm_workspace_bytes(M, N, K, 256) > L.tbik_gemm_static_scratch_bytes()
     x = torch.zeros(4096, dtype=torch.bfloat16, device="cuda")   # never dereferenced: the call is refused first
     rc = L.tbik_gemm_static(x.data_ptr(), x.data_ptr(), x.data_ptr(), M, N, K, K, K, N, _lib.DTYPE_BF16, 256,
