@@ -261,8 +261,8 @@ def main():
     peak, peak_src = load_peaks()
     achieved = dom_flops / (ms_dom * 1e-3) / 1e12
     # dram__bytes_read.sum + dram__bytes_write.sum of this launch from one ncu capture of this command
-    # (profiles/tree_gemm_128x256_m8192_dram_traffic.md); only known for the default shape
-    traffic = 1231.8e6 if (M == 8192 and tp == 1) else None
+    # (profiles/tree_gemm_pair256x128_m8192_dram_traffic.md); only known for the default shape
+    traffic = 1313.0e6 if (M == 8192 and tp == 1) else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "traffic": traffic, "kernel": "tree_gemm_kernel (down_proj shard)", "peak_source": peak_src,
                 "flops_per_launch": dom_flops, "ms_per_launch": ms_dom}
