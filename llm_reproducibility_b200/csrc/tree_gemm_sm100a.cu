@@ -1050,15 +1050,21 @@ static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int ma
   int ctas = sm_count();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   const int enough = ctas - ctas / 5;
-  const int order[5] = {2, 3, 1, 5, 6};
+  // short K (at most 6 leaves of 256): the per-tile costs (pipeline refill, storing C) weigh more than the
+  // k-loop, and the 256x256 pair tile has half as many of them per flop (measured: K = 512 981 vs 752 TFLOP/s,
+  // K = 1536 1251 vs 1077; from K = 2048 on the 256x128 pair tile wins)
+  const bool short_k = kblocks_total <= 24;
+  const int order[6] = {short_k ? 4 : 2, short_k ? 2 : 4, 3, 1, 5, 6};
+  constexpr int kOrder = 6;
   Plan best{};
   bool have = false;
-  for (int i = 0; i < 5; ++i) {
+  for (int i = 0; i < kOrder; ++i) {
+    if (!short_k && order[i] == 4) continue;  // long K: 256x256 only adds scratch need
     Plan pl = make_plan(order[i], M, N, L, max_ctas);
     if (pl.scratch_bytes > 0 && !(have_ws && pl.scratch_bytes <= ws_bytes)) continue;
     const Variant& pv = kVariants[order[i] - 1][pl.deep ? 1 : 0];
     if (pl.tiles_m * pl.tiles_n * (pv.pair ? 2 : 1) >= enough) {
-      if (order[i] <= 3 || !have_ws || groups < 2) return pl;  // enough rows of C: no slabs
+      if (order[i] <= 4 || !have_ws || groups < 2) return pl;  // enough rows of C: no slabs
       best = pl;
       have = true;
       break;
@@ -1071,7 +1077,8 @@ static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int ma
   if (!have) best = make_plan(1, M, N, L, max_ctas);
   if (!have_ws || groups < 2) return best;
   double best_cost = plan_cost_us(best, M, N, kblocks_total, ctas);
-  for (int i = 0; i < 5; ++i) {
+  for (int i = 0; i < kOrder; ++i) {
+    if (order[i] == 4) continue;
     for (int s = 2; s <= kMaxSplits && s <= groups; s *= 2) {
       Plan pl = make_plan(order[i], M, N, L, max_ctas, s);
       if (pl.tiles_m * pl.tiles_n * s * (kVariants[order[i] - 1][0].pair ? 2 : 1) > ctas) break;  // one wave only
