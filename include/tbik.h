@@ -137,6 +137,8 @@ typedef void* tbik_ar_t;
 #define TBIK_AR_CFG_MAX_BLOCKS 3        /* upper bound on CTAs per launch (0 = built-in)               */
 #define TBIK_AR_CFG_WAIT_LIMIT_NS 4     /* bound of one cross-GPU barrier wait                          */
 #define TBIK_AR_CFG_THREADS 5           /* threads per CTA, a multiple of 32 in [32, 512] (0 = built-in) */
+#define TBIK_AR_CFG_PUSH_MIN_BYTES 6    /* messages from this size on use the push schedule (0 = built-in, 1 = all two-shot sizes) */
+#define TBIK_AR_CFG_PUSH_CHUNKS 7       /* chunks the push schedule cuts a message into, 1..64 (0 = built-in) */
 
 /* Size in bytes of the signal (flag) area at the start of every rank's meta buffer.
  * Replaces: meta_size, mini_allreduce/tbik_kernel/csrc/allreduce/custom_all_reduce.cu:148-150. */

@@ -20,6 +20,10 @@ struct alignas(128) Signal {
   // fused GEMM + all-reduce: written by the owning rank, read by its peers
   uint32_t tile_ready[kMaxTiles];  // call number in which this rank's partial tile was last published
   uint32_t tile_done[kMaxTiles];   // call number in which this rank last finished reducing the tile it owns
+  // push schedule of the all-reduce: push_flag[b][r] is written by rank r's block b ("my reduced part of chunk c
+  // of call k is in your scratch": (k << 12) + c + 1); push_calls[b] is private to the owning rank
+  uint32_t push_flag[kMaxBlocks][kMaxRanks];
+  uint32_t push_calls[kMaxBlocks];
 };
 
 struct alignas(16) RankData {

@@ -12,6 +12,12 @@
 //   two-shot  GPU r reduces the r-th 1/n of the packs into its scratch area, a fenced barrier,
 //             then every GPU gathers the n reduced parts                      (bandwidth bound sizes)
 //
+//   push      two-shot whose second half does not pull: GPU r writes each reduced pack into its own result and
+//             into every peer's scratch, so the reduce phase (inbound direction of the links) and the
+//             distribution (outbound direction) run at the same time; a per-(block, source) flag tells the
+//             peer which chunks have landed, and the peer copies them from its scratch into its result
+//             locally                                                         (largest messages, n >= 4)
+//
 // Synchronisation is a per-block epoch barrier: block b of rank r stores its epoch into slot
 // [b][r] of every peer's flag array and waits until each of its own slots has reached the epoch
 // (wrap-safe signed compare, so one flag array serves consecutive barriers).  Every wait is
@@ -37,6 +43,7 @@ namespace tbik {
 
 constexpr int kThreads = 512;
 constexpr uint64_t kArWaitLimitNs = 2000000000ull;  // default bound of one barrier wait
+constexpr size_t kPushMinBytesDefault = ~size_t(0);   // push schedule: only when configured
 
 // One 16-byte pack reduced over the NG ranks.  TREE: rank-pair tree in T; else rank order in fp32.
 template <typename T, int NG, bool TREE>
@@ -132,6 +139,95 @@ allreduce_twoshot_kernel(const RankData* dp_ptr, RankSignals sg, Signal* self, v
   }
 }
 
+// Push schedule.  Every rank owns the r-th 1/n of the packs, cut into `chunks` chunks; every block works on the
+// same index set of every (chunk, part) on every rank, so block b of rank p only ever depends on block b of
+// the other ranks.  No barrier after the first one: by the time a rank has seen all its flags, every peer has
+// finished reading this rank's input and writing this rank's scratch.
+template <typename T, int NG, bool TREE>
+__global__ void __launch_bounds__(kThreads, 1)
+allreduce_push_kernel(const RankData* dp_ptr, RankSignals sg, Signal* self, void* out, int rank, int64_t npacks,
+                      ArStatus* status, uint64_t limit_ns, int chunks) {
+  __shared__ uint32_t fail;
+  __shared__ uint32_t base_s;
+  if (threadIdx.x == 0) {
+    fail = 0u;
+    // call counter kept on the device so that a captured graph advances it on every replay
+    const uint32_t k = self->push_calls[blockIdx.x] + 1u;
+    self->push_calls[blockIdx.x] = k;
+    base_s = k << 12;
+  }
+  const RankData dp = *dp_ptr;
+  uint4* scratch[NG];
+#pragma unroll
+  for (int r = 0; r < NG; ++r) scratch[r] = reinterpret_cast<uint4*>(sg.sig[r] + 1);
+  // every rank has entered this call: inputs are final, nobody still reads last call's scratch
+  if (!block_barrier<NG>(sg, self, rank, status, limit_ns, 1, &fail)) return;
+  const uint32_t base = base_s;
+  const int64_t part = npacks / NG;
+  const int64_t last_len = npacks - part * (NG - 1);
+  const int64_t clen = (last_len + chunks - 1) / chunks;
+  uint4* o = reinterpret_cast<uint4*>(out);
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t my_len = rank == NG - 1 ? last_len : part;
+  const int64_t my_start = rank * part;
+
+  auto reduce_chunk = [&](int c) {
+    const int64_t lo = c * clen;
+    int64_t hi = lo + clen;
+    if (hi > my_len) hi = my_len;
+    constexpr int kUnroll = 2;
+    int64_t idx = lo + tid;
+    for (; idx + (kUnroll - 1) * stride < hi; idx += kUnroll * stride) {
+      uint4 v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) v[u] = reduce_pack<T, NG, TREE>(dp, my_start + idx + u * stride);
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        o[my_start + idx + u * stride] = v[u];
+#pragma unroll
+        for (int p = 0; p < NG; ++p)
+          if (p != rank) scratch[p][my_start + idx + u * stride] = v[u];
+      }
+    }
+    for (; idx < hi; idx += stride) {
+      const uint4 v = reduce_pack<T, NG, TREE>(dp, my_start + idx);
+      o[my_start + idx] = v;
+#pragma unroll
+      for (int p = 0; p < NG; ++p)
+        if (p != rank) scratch[p][my_start + idx] = v;
+    }
+    __syncthreads();  // the block's stores are ordered before the releases below
+    if (threadIdx.x < NG && static_cast<int>(threadIdx.x) != rank)
+      st_flag_release(&sg.sig[threadIdx.x]->push_flag[blockIdx.x][rank], base + static_cast<uint32_t>(c) + 1u);
+  };
+  auto gather_chunk = [&](int c) -> bool {
+    if (threadIdx.x < NG && static_cast<int>(threadIdx.x) != rank) {
+      if (!wait_flag_reached(&self->push_flag[blockIdx.x][threadIdx.x], base + static_cast<uint32_t>(c) + 1u, status,
+                             limit_ns, rank, threadIdx.x, 4))
+        fail = 1u;
+    }
+    __syncthreads();
+    if (fail != 0u) return false;
+    const int64_t lo = c * clen;
+#pragma unroll
+    for (int src = 0; src < NG; ++src) {
+      if (src == rank) continue;
+      int64_t hi = lo + clen;
+      const int64_t len = src == NG - 1 ? last_len : part;
+      if (hi > len) hi = len;
+      const int64_t start = src * part;
+      for (int64_t idx = lo + tid; idx < hi; idx += stride) o[start + idx] = ld_pack(scratch[rank] + start + idx);
+    }
+    return true;
+  };
+  for (int c = 0; c < chunks; ++c) {
+    reduce_chunk(c);
+    if (c >= 1 && !gather_chunk(c - 1)) return;
+  }
+  gather_chunk(chunks - 1);
+}
+
 // ==================================================================== host object
 struct IpcKey {
   unsigned char b[sizeof(cudaIpcMemHandle_t)];
@@ -153,6 +249,8 @@ struct Communicator {
   size_t oneshot_max_bytes = 0;  // 0 = built-in policy
   int max_blocks = 0;            // 0 = built-in policy
   int threads = 0;               // 0 = built-in policy
+  size_t push_min_bytes = 0;     // 0 = built-in policy
+  int push_chunks = 0;           // 0 = built-in policy
   uint64_t wait_limit_ns = kArWaitLimitNs;
   ArStatus* status_host = nullptr;
   ArStatus* status_dev = nullptr;
@@ -165,8 +263,12 @@ static Communicator* as_comm(tbik_ar_t h) { return reinterpret_cast<Communicator
 
 template <typename T, int NG, bool TREE>
 static int launch_ar(Communicator* c, const RankData* slot, void* out, int64_t npacks, bool twoshot, int blocks,
-                     int threads, cudaStream_t stream) {
-  if (twoshot)
+                     int threads, cudaStream_t stream, int push_chunks = 0) {
+  if (push_chunks > 0) {
+    if constexpr (NG >= 2)
+      allreduce_push_kernel<T, NG, TREE><<<blocks, threads, 0, stream>>>(slot, c->sg, c->self, out, c->rank, npacks,
+                                                                          c->status_dev, c->wait_limit_ns, push_chunks);
+  } else if (twoshot)
     allreduce_twoshot_kernel<T, NG, TREE><<<blocks, threads, 0, stream>>>(slot, c->sg, c->self, out, c->rank, npacks,
                                                                             c->status_dev, c->wait_limit_ns);
   else
@@ -179,17 +281,17 @@ static int launch_ar(Communicator* c, const RankData* slot, void* out, int64_t n
 
 template <typename T, bool TREE>
 static int dispatch_world(Communicator* c, const RankData* slot, void* out, int64_t npacks, bool twoshot, int blocks,
-                          int threads, cudaStream_t stream) {
+                          int threads, cudaStream_t stream, int push_chunks) {
   switch (c->world) {
     case 1:
       if constexpr (TREE) return launch_ar<T, 1, TREE>(c, slot, out, npacks, false, blocks, threads, stream);
       break;
-    case 2: return launch_ar<T, 2, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream);
-    case 4: return launch_ar<T, 4, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream);
+    case 2: return launch_ar<T, 2, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks);
+    case 4: return launch_ar<T, 4, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks);
     case 6:
-      if constexpr (!TREE) return launch_ar<T, 6, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream);
+      if constexpr (!TREE) return launch_ar<T, 6, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks);
       break;
-    case 8: return launch_ar<T, 8, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream);
+    case 8: return launch_ar<T, 8, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks);
     default: break;
   }
   return set_error(TBIK_ERR_SHAPE, TREE ? "tree all-reduce supports 1, 2, 4 or 8 ranks"
@@ -257,6 +359,16 @@ int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, vo
       else return set_error(TBIK_ERR_SHAPE, "all-reduce: message needs more scratch than the meta buffer provides (raise max_size)");
     }
   }
+  // push schedule: needs room for the whole message in every rank's scratch
+  int push_chunks = 0;
+  {
+    const size_t push_min = c->push_min_bytes != 0 ? c->push_min_bytes : kPushMinBytesDefault;
+    if (twoshot && bytes >= push_min && bytes <= c->scratch_bytes) {
+      push_chunks = c->push_chunks > 0 ? c->push_chunks : 4;
+      const int64_t part = npacks / c->world;
+      if (push_chunks > part) push_chunks = part > 0 ? static_cast<int>(part) : 1;
+    }
+  }
   const int64_t work = twoshot ? (npacks + c->world - 1) / c->world : npacks;
   int cap_blocks = c->max_blocks > 0 ? c->max_blocks : (bytes <= (256u << 10) ? 36 : c->sm_count);
   if (cap_blocks > kMaxBlocks) cap_blocks = kMaxBlocks;
@@ -267,13 +379,13 @@ int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, vo
   if (blocks < 1) blocks = 1;
 
   if (dtype == TBIK_DTYPE_FP32)
-    return tree ? dispatch_world<float, true>(c, slot, out, npacks, twoshot, blocks, threads, stream)
-                : dispatch_world<float, false>(c, slot, out, npacks, twoshot, blocks, threads, stream);
+    return tree ? dispatch_world<float, true>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks)
+                : dispatch_world<float, false>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks);
   if (dtype == TBIK_DTYPE_FP16)
-    return tree ? dispatch_world<__half, true>(c, slot, out, npacks, twoshot, blocks, threads, stream)
-                : dispatch_world<__half, false>(c, slot, out, npacks, twoshot, blocks, threads, stream);
-  return tree ? dispatch_world<__nv_bfloat16, true>(c, slot, out, npacks, twoshot, blocks, threads, stream)
-              : dispatch_world<__nv_bfloat16, false>(c, slot, out, npacks, twoshot, blocks, threads, stream);
+    return tree ? dispatch_world<__half, true>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks)
+                : dispatch_world<__half, false>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks);
+  return tree ? dispatch_world<__nv_bfloat16, true>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks)
+              : dispatch_world<__nv_bfloat16, false>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks);
 }
 
 int ar_gemm_tree_allreduce(tbik_ar_t h, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
@@ -368,6 +480,11 @@ int ar_configure(tbik_ar_t h, int key, int64_t value) {
     case TBIK_AR_CFG_ONESHOT_MAX_BYTES: c->oneshot_max_bytes = static_cast<size_t>(value); return TBIK_OK;
     case TBIK_AR_CFG_MAX_BLOCKS: c->max_blocks = static_cast<int>(value); return TBIK_OK;
     case TBIK_AR_CFG_WAIT_LIMIT_NS: c->wait_limit_ns = static_cast<uint64_t>(value); return TBIK_OK;
+    case TBIK_AR_CFG_PUSH_MIN_BYTES: c->push_min_bytes = static_cast<size_t>(value); return TBIK_OK;
+    case TBIK_AR_CFG_PUSH_CHUNKS:
+      if (value < 0 || value > 64) return set_error(TBIK_ERR_ARG, "tbik_ar_configure: push chunks must be 0..64");
+      c->push_chunks = static_cast<int>(value);
+      return TBIK_OK;
     case TBIK_AR_CFG_THREADS:
       if (value != 0 && (value < 32 || value > kThreads || value % 32 != 0))
         return set_error(TBIK_ERR_ARG, "tbik_ar_configure: threads must be a multiple of 32 in [32, 512]");

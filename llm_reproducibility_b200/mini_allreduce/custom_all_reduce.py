@@ -108,6 +108,10 @@ class CustomAllreduce:
         self.rank_data = torch.empty(8 * 1024 * 1024, dtype=torch.uint8, device=self.device)
         self._ptr = ops.init_custom_ar(self.meta_ptrs, self.rank_data, rank, self.full_nvlink)
         ops.configure(self._ptr, ops.CFG_SCRATCH_BYTES, max_size)
+        # optional: messages from this many bytes on use the push schedule (see tbik.h, TBIK_AR_CFG_PUSH_MIN_BYTES)
+        push_min = int(os.environ.get("TBIK_AR_PUSH_MIN_BYTES", "0"))
+        if push_min > 0:
+            ops.configure(self._ptr, ops.CFG_PUSH_MIN_BYTES, push_min)
         ops.register_buffer(self._ptr, self.buffer_ptrs)
         self.disabled = False
 

@@ -63,6 +63,7 @@ def tree_matmul_allreduce(fa: int, A: torch.Tensor, B: torch.Tensor, reg_buffer:
 
 # keys of `configure`
 CFG_SCRATCH_BYTES, CFG_ONESHOT_MAX_BYTES, CFG_MAX_BLOCKS, CFG_WAIT_LIMIT_NS, CFG_THREADS = 1, 2, 3, 4, 5
+CFG_PUSH_MIN_BYTES, CFG_PUSH_CHUNKS = 6, 7
 
 
 def configure(fa: int, key: int, value: int) -> None:

@@ -32,10 +32,13 @@ def tree_allreduce_parity(rank, world, cases, max_size):
     for (numel, dtype, seed) in cases:
         xs = _inputs(world, numel, dtype, seed, device)
         want = tree_allreduce_ref(xs)
-        for mode, one_max in (("auto", 0), ("oneshot", 1 << 40), ("twoshot", 1)):
+        for mode, one_max, push_min, chunks in (("auto", 0, 0, 0), ("oneshot", 1 << 40, 0, 0), ("twoshot", 1, 1 << 60, 0),
+                                                ("push", 1, 1, 0), ("push1", 1, 1, 1), ("push7", 1, 1, 7)):
             if mode == "oneshot" and numel * xs[0].element_size() > (8 << 20):
                 continue
             ops.configure(ar._ptr, ops.CFG_ONESHOT_MAX_BYTES, one_max)
+            ops.configure(ar._ptr, ops.CFG_PUSH_MIN_BYTES, push_min)
+            ops.configure(ar._ptr, ops.CFG_PUSH_CHUNKS, chunks)
             got = ar.custom_tree_all_reduce(xs[rank])
             assert got is not None, (numel, dtype)
             torch.cuda.synchronize()
@@ -44,6 +47,8 @@ def tree_allreduce_parity(rank, world, cases, max_size):
             report.append((numel, str(dtype), mode, ok))
             assert ok, f"rank {rank}: tree all-reduce differs from oracle: numel={numel} {dtype} {mode}"
         ops.configure(ar._ptr, ops.CFG_ONESHOT_MAX_BYTES, 0)
+        ops.configure(ar._ptr, ops.CFG_PUSH_MIN_BYTES, 0)
+        ops.configure(ar._ptr, ops.CFG_PUSH_CHUNKS, 0)
         # the reference's own cross-check: custom kernel vs all_gather + ordered adds
         native = tree_all_reduce_sum_native(xs[rank], None)
         assert torch.equal(bits(native), bits(want))
@@ -54,6 +59,20 @@ def tree_allreduce_parity(rank, world, cases, max_size):
         got = ar.custom_tree_all_reduce(xs[rank])
     torch.cuda.synchronize()
     assert torch.equal(bits(got), bits(want))
+    # the same with the push schedule, alternating inputs so that a stale chunk in the scratch would show
+    ops.configure(ar._ptr, ops.CFG_ONESHOT_MAX_BYTES, 1)
+    ops.configure(ar._ptr, ops.CFG_PUSH_MIN_BYTES, 1)
+    ys = _inputs(world, 1 << 18, torch.bfloat16, 78, device)
+    zs = _inputs(world, 1 << 18, torch.bfloat16, 79, device)
+    want_y, want_z = tree_allreduce_ref(ys), tree_allreduce_ref(zs)
+    for i in range(20):
+        got_y = ar.custom_tree_all_reduce(ys[rank])
+        got_z = ar.custom_tree_all_reduce(zs[rank])
+    torch.cuda.synchronize()
+    ar.check_status()
+    assert torch.equal(bits(got_y), bits(want_y)) and torch.equal(bits(got_z), bits(want_z))
+    ops.configure(ar._ptr, ops.CFG_ONESHOT_MAX_BYTES, 0)
+    ops.configure(ar._ptr, ops.CFG_PUSH_MIN_BYTES, 0)
     # ineligible inputs return None (odd byte size; too large)
     assert ar.custom_tree_all_reduce(torch.zeros(3, dtype=torch.bfloat16, device=device)) is None
     assert ar.custom_tree_all_reduce(torch.zeros(max_size, dtype=torch.uint8, device=device).view(torch.bfloat16)) is None

@@ -3,7 +3,7 @@ against NCCL all_reduce and the all_gather + ordered-adds path, bf16, 8 KB ... 6
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         tests/bench_allreduce.py [--iters 20] [--warmup 5] [--max-mb 64] [--min-kb 8]
-                                 [--oneshot-max-kb K] [--max-blocks B] [--threads T] [--only-p2p]
+                                 [--oneshot-max-kb K] [--max-blocks B] [--threads T] [--push-min-kb K] [--push-chunks C] [--only-p2p]
 
 --oneshot-max-kb / --max-blocks override the built-in schedule choice (for tuning sweeps).
 
@@ -32,6 +32,8 @@ def main():
     ap.add_argument("--oneshot-max-kb", type=int, default=0)
     ap.add_argument("--max-blocks", type=int, default=0)
     ap.add_argument("--threads", type=int, default=0)
+    ap.add_argument("--push-min-kb", type=int, default=0)
+    ap.add_argument("--push-chunks", type=int, default=0)
     ap.add_argument("--only-p2p", action="store_true")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -48,6 +50,10 @@ def main():
     from llm_reproducibility_b200.mini_allreduce import custom_all_reduce_ops as ops
     if args.oneshot_max_kb:
         ops.configure(ar._ptr, ops.CFG_ONESHOT_MAX_BYTES, args.oneshot_max_kb << 10)
+    if args.push_min_kb:
+        ops.configure(ar._ptr, ops.CFG_PUSH_MIN_BYTES, args.push_min_kb << 10)
+    if args.push_chunks:
+        ops.configure(ar._ptr, ops.CFG_PUSH_CHUNKS, args.push_chunks)
     if args.threads:
         ops.configure(ar._ptr, ops.CFG_THREADS, args.threads)
     if args.max_blocks:
