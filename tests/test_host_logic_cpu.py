@@ -52,6 +52,25 @@ def test_cabi_calls_that_need_no_gpu():
     assert L.tbik_ar_create(sig, 2, 5, 1, 1 << 20, 1, ctypes.byref(out)) == -1 and "invalid rank" in _lib.last_error()
 
 
+def test_k_slab_plan_queries_need_no_gpu():
+    """Which (tiling, slabs) combinations exist and what scratch they need is host arithmetic."""
+    from llm_reproducibility_b200 import _lib
+    L = _lib.lib()
+    need = L.tbik_gemm_slabs_workspace_bytes
+    M, N, K = 16, 4096, 12288                       # T = 48, F = 3: 16 level-0 groups
+    for tiling in range(1, 7):
+        sizes = [need(M, N, K, 256, tiling, s) for s in (2, 4, 8, 16)]
+        assert all(b >= s * M * N * 2 for b, s in zip(sizes, (2, 4, 8, 16))), (tiling, sizes)   # room for every root
+        assert sizes == sorted(sizes)
+        assert need(M, N, K, 256, tiling, 32) == 0   # more than 16 slabs
+        assert need(M, N, K, 256, tiling, 3) == 0    # not a power of two
+    assert need(M, N, 1536, 256, 1, 4) == 0          # T = 6, F = 3: only two whole subtrees
+    assert need(M, N, 1536, 256, 1, 2) >= 2 * M * N * 2
+    assert need(M, N, K, 256, 0, 2) == 0 and need(M, N, K, 256, 7, 2) == 0   # tiling out of range
+    assert need(M, N, 1000, 256, 1, 2) == 0          # K not a multiple of the leaf
+    assert need(M, 4090, K, 256, 1, 2) >= 2 * M * 4096 * 2                   # rows of the roots padded to 8 columns
+
+
 def test_oracle_tree_shape_agrees_with_library():
     from llm_reproducibility_b200.tbik.tree_based_matmul import tree_shape as lib_shape
     from oracle.tbik_ref import tree_shape
