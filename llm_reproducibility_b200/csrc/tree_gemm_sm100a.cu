@@ -602,7 +602,8 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // C leaves through the TMA unit when possible: the finished tile is staged (128-byte swizzle) in the
     // shared-memory slot of stack level 1, which is free once the tree is complete, and one thread issues
     // one tiled store per 64 columns.  The slot may only be rewritten after those stores have read it.
-    const bool tma_c = SLEVELS > 0 && p.tma_store != 0;
+    // (not in a CTA pair: there the staged path produced torn 16-byte words at short K, see auto_plan)
+    const bool tma_c = SLEVELS > 0 && !PAIR && p.tma_store != 0;
     bool staging_busy = false;
     bool ok = true;
     uint32_t epi_phase = 0;
@@ -1026,14 +1027,16 @@ static Plan make_plan(int tiling, int M, int N, int L, int max_ctas, int splits 
   return pl;
 }
 
-// Rough time of a plan in microseconds, from measurements at few rows of C: a CTA advances one 64-wide k-block every
-// 0.30 us (0.47 us for 256-column tiles) whatever the tile width, so what counts is the k-blocks per CTA.
+// Rough time of a plan in microseconds, fitted to measurements at 16..512 rows of C (N = 4096, K = 1536..12288):
+// a CTA advances one 64-wide k-block every 0.155 us (32-column tile) .. 0.53 us (256 columns), launch and
+// prologue cost 3.5 us, the combine kernel 2.5 us plus its bytes.  What counts is the k-blocks per CTA.
 static double plan_cost_us(const Plan& pl, int M, int N, int kblocks_total, int ctas) {
   const Variant& v = kVariants[pl.tiling - 1][pl.deep ? 1 : 0];
   const int items = pl.tiles_m * pl.tiles_n * pl.splits;
   const int units = v.pair ? ctas / 2 : ctas;
   const int waves = (items + units - 1) / (units > 0 ? units : 1);
-  double t = 4.0 + waves * (kblocks_total / pl.splits) * (v.bn >= 256 ? 0.47 : 0.30);
+  const double per_kblock = v.bn >= 256 ? 0.53 : v.bn == 128 ? (v.pair ? 0.18 : 0.23) : v.bn == 64 ? 0.17 : 0.155;
+  double t = 3.5 + waves * (kblocks_total / pl.splits) * per_kblock;
   if (pl.splits > 1) t += 2.5 + static_cast<double>(pl.splits + 1) * M * N * 2 / 3.0e6;  // combine launch + its bytes at 3 TB/s
   return t;
 }
@@ -1050,21 +1053,19 @@ static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int ma
   int ctas = sm_count();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   const int enough = ctas - ctas / 5;
-  // short K (at most 6 leaves of 256): the per-tile costs (pipeline refill, storing C) weigh more than the
-  // k-loop, and the 256x256 pair tile has half as many of them per flop (measured: K = 512 981 vs 752 TFLOP/s,
-  // K = 1536 1251 vs 1077; from K = 2048 on the 256x128 pair tile wins)
-  const bool short_k = kblocks_total <= 24;
-  const int order[6] = {short_k ? 4 : 2, short_k ? 2 : 4, 3, 1, 5, 6};
-  constexpr int kOrder = 6;
+  // The 256x256 pair tiling is not in the list: it is faster at K <= 1536 (981 vs 752 TFLOP/s at K = 512) but
+  // with its staged TMA stores it returned wrong words in a few tiles at M >= 2048, K = 1024 (a race that
+  // reading the code has not explained); it now stores C directly and is kept for explicit requests only.
+  const int order[5] = {2, 3, 1, 5, 6};
+  constexpr int kOrder = 5;
   Plan best{};
   bool have = false;
   for (int i = 0; i < kOrder; ++i) {
-    if (!short_k && order[i] == 4) continue;  // long K: 256x256 only adds scratch need
     Plan pl = make_plan(order[i], M, N, L, max_ctas);
     if (pl.scratch_bytes > 0 && !(have_ws && pl.scratch_bytes <= ws_bytes)) continue;
     const Variant& pv = kVariants[order[i] - 1][pl.deep ? 1 : 0];
     if (pl.tiles_m * pl.tiles_n * (pv.pair ? 2 : 1) >= enough) {
-      if (order[i] <= 4 || !have_ws || groups < 2) return pl;  // enough rows of C: no slabs
+      if (order[i] <= 3 || !have_ws || groups < 2) return pl;  // enough rows of C: no slabs
       best = pl;
       have = true;
       break;
@@ -1078,7 +1079,6 @@ static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int ma
   if (!have_ws || groups < 2) return best;
   double best_cost = plan_cost_us(best, M, N, kblocks_total, ctas);
   for (int i = 0; i < kOrder; ++i) {
-    if (order[i] == 4) continue;
     for (int s = 2; s <= kMaxSplits && s <= groups; s *= 2) {
       Plan pl = make_plan(order[i], M, N, L, max_ctas, s);
       if (pl.tiles_m * pl.tiles_n * s * (kVariants[order[i] - 1][0].pair ? 2 : 1) > ctas) break;  // one wave only

@@ -227,6 +227,22 @@ def test_result_does_not_depend_on_cta_count(tiling):
         assert torch.equal(bits(C), bits(outs[0]))
 
 
+@pytest.mark.parametrize("K", [512, 1024, 1536])
+def test_short_k_many_tiles_every_tiling_repeatedly(K):
+    """Tensor-parallel shard shapes: few leaves per tile, many tiles per CTA, so tile hand-overs (accumulator buffers,
+    stack slot, staged stores of C) happen every few microseconds.  Every tiling, three times, same bits."""
+    M, N = 2048, 4096
+    g = torch.Generator(device="cuda").manual_seed(K)
+    A = torch.randn(M, K, generator=g, device="cuda").to(torch.bfloat16)
+    W = (torch.randn(N, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    one = _gemm_ex(A, W, M, N, K, 0, 1)
+    for tiling in TILINGS:
+        for rep in range(3):
+            assert torch.equal(bits(one), bits(_gemm_ex(A, W, M, N, K, 0, tiling))), (tiling, rep)
+    auto = _gemm_ex(A, W, M, N, K, 0, 0)
+    assert torch.equal(bits(one), bits(auto))
+
+
 def _gemm_slabs(Ad, W, M, N, K, tiling, slabs, dtype_code=0, leaf=256, ldc=None):
     from llm_reproducibility_b200 import _lib
     L = _lib.lib()
