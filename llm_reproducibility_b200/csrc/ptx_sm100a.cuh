@@ -116,17 +116,6 @@ TBIK_DEVICE bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile uint3
   }
 }
 
-// The same wait for a whole (converged) warp: lane 0 polls, the others sleep in the shuffle that
-// hands them the outcome.  32 lanes polling one mbarrier word are 32 requests per poll to the shared
-// memory unit; eight such warps slow down every barrier operation of the CTA, the TMA producer's and
-// the UMMA issuer's included.
-TBIK_DEVICE bool mbar_wait_bounded_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                        uint64_t limit_ns) {
-  uint32_t ok = 1u;
-  if ((threadIdx.x & 31u) == 0u) ok = mbar_wait_bounded(bar, parity, abort_flag, limit_ns) ? 1u : 0u;
-  return __shfl_sync(0xffffffffu, ok, 0) != 0u;
-}
-
 // ---------------------------------------------------------------- TMA (tiled, 2-D, one CTA)
 TBIK_DEVICE void prefetch_tensormap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

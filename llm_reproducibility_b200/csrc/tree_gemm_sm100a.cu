@@ -602,17 +602,19 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // C leaves through the TMA unit when possible: the finished tile is staged (128-byte swizzle) in the
     // shared-memory slot of stack level 1, which is free once the tree is complete, and one thread issues
     // one tiled store per 64 columns.  The slot may only be rewritten after those stores have read it.
-    // (not in a CTA pair: there the staged path produced torn 16-byte words at short K, see auto_plan)
-    const bool tma_c = SLEVELS > 0 && !PAIR && p.tma_store != 0;
+    const bool tma_c = SLEVELS > 0 && p.tma_store != 0;
     bool staging_busy = false;
     bool ok = true;
     uint32_t epi_phase = 0;
     // Rendezvous of the eight epilogue warps on an mbarrier with a bounded wait (a plain bar.sync would
-    // wait forever for a warp that has left after an abort).
+    // wait forever for a warp that has left after an abort).  Every lane waits on the barrier itself: a
+    // variant in which lane 0 polled and handed the outcome to the others with a shuffle left lanes 1..31
+    // without an acquire, and in a CTA pair the staged tile was then read or rewritten too early (torn
+    // 16-byte words in C at four leaves per tile).
     auto epi_sync = [&]() {
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_base + C_::OFF_EPI_BAR);
-      if (!mbar_wait_bounded_warp(smem_base + C_::OFF_EPI_BAR, epi_phase, abort_flag, WAIT_LIMIT_NS)) {
+      if (!mbar_wait_bounded(smem_base + C_::OFF_EPI_BAR, epi_phase, abort_flag, WAIT_LIMIT_NS)) {
         ok = false;
         role_failed = 6;
       }
@@ -645,7 +647,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
         for (int leaf = 0; ok && leaf < p.T; ++leaf, ++ctr) {
           const uint32_t a = ctr & 1u;
-          if (!mbar_wait_bounded_warp(tfull_bar(a), (ctr >> 1) & 1u, abort_flag, WAIT_LIMIT_NS)) {
+          if (!mbar_wait_bounded(tfull_bar(a), (ctr >> 1) & 1u, abort_flag, WAIT_LIMIT_NS)) {
             ok = false;
             role_failed = 4;
             break;
@@ -667,7 +669,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int leaf = 0; ok && leaf < p.T; ++leaf, ++leaf_ctr) {
         const uint32_t a = leaf_ctr & 1u;
         const uint32_t aphase = (leaf_ctr >> 1) & 1u;
-        if (!mbar_wait_bounded_warp(tfull_bar(a), aphase, abort_flag, WAIT_LIMIT_NS)) {
+        if (!mbar_wait_bounded(tfull_bar(a), aphase, abort_flag, WAIT_LIMIT_NS)) {
           ok = false;
           role_failed = 4;
           break;
@@ -1053,19 +1055,21 @@ static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int ma
   int ctas = sm_count();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   const int enough = ctas - ctas / 5;
-  // The 256x256 pair tiling is not in the list: it is faster at K <= 1536 (981 vs 752 TFLOP/s at K = 512) but
-  // with its staged TMA stores it returned wrong words in a few tiles at M >= 2048, K = 1024 (a race that
-  // reading the code has not explained); it now stores C directly and is kept for explicit requests only.
-  const int order[5] = {2, 3, 1, 5, 6};
-  constexpr int kOrder = 5;
+  // short K (at most 6 leaves of 256): the per-tile costs (pipeline refill, storing C) weigh more than the
+  // k-loop, and the 256x256 pair tile has half as many of them per flop (measured: K = 512 981 vs 752 TFLOP/s,
+  // K = 1536 1251 vs 1077; from K = 2048 on the 256x128 pair tile wins)
+  const bool short_k = kblocks_total <= 24;
+  const int order[6] = {short_k ? 4 : 2, short_k ? 2 : 4, 3, 1, 5, 6};
+  constexpr int kOrder = 6;
   Plan best{};
   bool have = false;
   for (int i = 0; i < kOrder; ++i) {
+    if (!short_k && order[i] == 4) continue;  // long K: 256x256 only adds scratch need
     Plan pl = make_plan(order[i], M, N, L, max_ctas);
     if (pl.scratch_bytes > 0 && !(have_ws && pl.scratch_bytes <= ws_bytes)) continue;
     const Variant& pv = kVariants[order[i] - 1][pl.deep ? 1 : 0];
     if (pl.tiles_m * pl.tiles_n * (pv.pair ? 2 : 1) >= enough) {
-      if (order[i] <= 3 || !have_ws || groups < 2) return pl;  // enough rows of C: no slabs
+      if (order[i] <= 4 || !have_ws || groups < 2) return pl;  // enough rows of C: no slabs
       best = pl;
       have = true;
       break;
@@ -1079,6 +1083,7 @@ static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int ma
   if (!have_ws || groups < 2) return best;
   double best_cost = plan_cost_us(best, M, N, kblocks_total, ctas);
   for (int i = 0; i < kOrder; ++i) {
+    if (order[i] == 4) continue;
     for (int s = 2; s <= kMaxSplits && s <= groups; s *= 2) {
       Plan pl = make_plan(order[i], M, N, L, max_ctas, s);
       if (pl.tiles_m * pl.tiles_n * s * (kVariants[order[i] - 1][0].pair ? 2 : 1) > ctas) break;  // one wave only
