@@ -58,8 +58,8 @@ int tbik_tree_shape(int64_t K, int leaf, int* T, int* F, int* L);
  *   node_dtype  TBIK_NODE_INPUT
  * A and W must be 16-byte aligned with lda, ldw multiples of 8.  M == 0 or N == 0 is a no-op.
  * The kernel is enqueued on `stream`.  This entry point uses no scratch memory and allocates
- * nothing: it runs the 128x128 tiling, whose tree stack fits on chip for trees of up to 7 levels
- * (K <= 64 * 2 * leaf); deeper trees are rejected here and need tbik_gemm_ws.
+ * nothing: it picks among the tilings whose tree stack fits on chip (128-column tiles: trees of up to
+ * 7 levels, K <= 64 * 2 * leaf); deeper trees are rejected here and need tbik_gemm_ws.
  * Replaces: matmul_tp_persistent / matmul_kernel_tp_persistent,
  *           src/tbik/tree_based_matmul.py:50-187 and :190-274. */
 int tbik_gemm(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
@@ -70,10 +70,11 @@ int tbik_gemm(const void* A, const void* W, void* C, int M, int N, int K, int64_
 size_t tbik_gemm_workspace_bytes(int M, int N, int64_t K, int leaf);
 
 /* As tbik_gemm, with a caller-owned scratch buffer (16-byte aligned device memory, contents
- * irrelevant before and after the call, not shared with a concurrently running call).  With
- * enough scratch the faster 128x256 tiling is used for M > 128: its accumulators fill tensor
- * memory, so the upper levels of the tree stack are kept in shared memory and, for levels touched
- * at most once every four leaves, in this buffer.  Same bits as tbik_gemm.
+ * irrelevant before and after the call, not shared with a concurrently running call).  The
+ * scratch serves the 256-column tilings (their accumulators fill tensor memory, so the upper
+ * levels of the tree stack are kept in shared memory and, for levels touched at most once every
+ * four leaves, in this buffer), trees deeper than the on-chip stack, and the K-slab roots of
+ * decode-sized calls (below).  Same bits as tbik_gemm.
  * Replaces: the same reference functions as tbik_gemm. */
 int tbik_gemm_ws(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
                  int dtype, int leaf, int node_dtype, void* workspace, size_t workspace_bytes, tbik_stream_t stream);

@@ -53,6 +53,24 @@ def _workspace(device: torch.device, stream: int, nbytes: int) -> Optional[torch
     return ws
 
 
+_WS_NEED = {}  # (device index, M, N, K, leaf) -> bytes of scratch the automatic schedule wants
+
+
+def _launch(A, W, C, M, N, K, leaf, dev) -> int:
+    """Enqueue the GEMM on the current stream of `dev` (which must be the current device)."""
+    L = _lib.lib()
+    key = (dev.index, M, N, K, leaf)
+    need = _WS_NEED.get(key)
+    if need is None:
+        need = _WS_NEED[key] = int(L.tbik_gemm_workspace_bytes(M, N, K, leaf))
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ws = _workspace(dev, stream, need)
+    return L.tbik_gemm_ws(A.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K,
+                          max(A.stride(0), K), max(W.stride(0), K), max(C.stride(0), N),
+                          _DTYPE_CODE[A.dtype], leaf, _lib.NODE_INPUT,
+                          ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, stream)
+
+
 def prepare_operands(A: torch.Tensor, B: torch.Tensor):
     """(A', W) in the layout the kernels take: A' row-major with aligned rows, W = B^T with K contiguous."""
     M, K = A.shape
@@ -84,15 +102,14 @@ def matmul_tp_persistent(A: torch.Tensor, B: torch.Tensor, bias: Optional[torch.
     W = _k_major_weight(B)
     C = out if out is not None else torch.empty((M, N), device=A.device, dtype=A.dtype)
     assert C.shape == (M, N) and C.stride(1) == 1 and C.dtype == A.dtype
-    with torch.cuda.device(A.device):
-        stream = torch.cuda.current_stream().cuda_stream
-        L = _lib.lib()
-        ws = _workspace(A.device, stream, int(L.tbik_gemm_workspace_bytes(M, N, K, leaf)))
-        rc = L.tbik_gemm_ws(A.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K,
-                            max(A.stride(0), K), max(W.stride(0), K), max(C.stride(0), N),
-                            _DTYPE_CODE[A.dtype], leaf, _lib.NODE_INPUT,
-                            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, stream)
-    _lib.check(rc, "tbik_gemm_ws")
+    dev = A.device
+    if torch.cuda.current_device() == dev.index:
+        rc = _launch(A, W, C, M, N, K, leaf, dev)
+    else:
+        with torch.cuda.device(dev):
+            rc = _launch(A, W, C, M, N, K, leaf, dev)
+    if rc != 0:
+        _lib.check(rc, "tbik_gemm_ws")
     if bias is not None:
         C += bias
     return C
