@@ -52,6 +52,17 @@ def test_cabi_calls_that_need_no_gpu():
     assert L.tbik_ar_create(sig, 2, 5, 1, 1 << 20, 1, ctypes.byref(out)) == -1 and "invalid rank" in _lib.last_error()
 
 
+def test_product_never_touches_the_oracle_or_a_cpu_fallback():
+    """The oracle is test infrastructure: nothing under the package may import, read or run it."""
+    pkg = os.path.join(ROOT, "llm_reproducibility_b200")
+    for base, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(base, f), encoding="utf-8").read()
+                assert "oracle" not in text, os.path.join(base, f)
+                assert "_work" not in text, os.path.join(base, f)
+
+
 def test_k_slab_plan_queries_need_no_gpu():
     """Which (tiling, slabs) combinations exist and what scratch they need is host arithmetic."""
     from llm_reproducibility_b200 import _lib
