@@ -60,7 +60,7 @@ def test_product_never_touches_the_oracle_or_a_cpu_fallback():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(base, f), encoding="utf-8").read()
                 assert "oracle" not in text, os.path.join(base, f)
-                assert "_work" not in text, os.path.join(base, f)
+                assert "_work/" not in text, os.path.join(base, f)
 
 
 def test_k_slab_plan_queries_need_no_gpu():
