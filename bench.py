@@ -196,6 +196,9 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # keep stdout to the one JSON line: NCCL prints its version banner there at NCCL_DEBUG=VERSION
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=dev)
     M, tp = args.m, world
 
@@ -270,16 +273,39 @@ def main():
     # ---- end to end through the public API with host activations
     host_in = [torch.randn(M, K // tp).to(torch.bfloat16).pin_memory() for _, K, _ in LAYERS]
     host_out = [torch.empty(M, N, dtype=torch.bfloat16).pin_memory() for _, _, N in LAYERS]
-    dev_in = [torch.empty(M, K // tp, dtype=torch.bfloat16, device=dev) for _, K, _ in LAYERS]
+    # The copies run on two copy streams beside the compute stream, inputs double-buffered on the device: the
+    # host->device copy of step i+1 overlaps the GEMMs and the device->host copy of step i.  Every step still
+    # moves its own inputs in and its own results out inside the timed region.
+    NBUF = 2
+    dev_in = [[torch.empty(M, K // tp, dtype=torch.bfloat16, device=dev) for _, K, _ in LAYERS] for _ in range(NBUF)]
+    in_free = [[None] * len(LAYERS) for _ in range(NBUF)]   # event: the compute that last read dev_in[b][li]
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
 
     def e2e_step(i):
+        b = i % NBUF
+        cur = torch.cuda.current_stream()
+        leaving = []
         for li, (X, W, C) in enumerate(sets[i % nsets]):
-            dev_in[li].copy_(host_in[li], non_blocking=True)
+            with torch.cuda.stream(s_in):
+                if in_free[b][li] is not None:
+                    s_in.wait_event(in_free[b][li])
+                dev_in[b][li].copy_(host_in[li], non_blocking=True)
+                arrived = s_in.record_event()
+            cur.wait_event(arrived)
             if tp > 1:
-                out = tree_matmul_all_reduce(dev_in[li], W.t(), None)
+                out = tree_matmul_all_reduce(dev_in[b][li], W.t(), None)
             else:
-                out = matmul_tp_persistent(dev_in[li], W.t(), out=C)
-            host_out[li].copy_(out, non_blocking=True)
+                out = matmul_tp_persistent(dev_in[b][li], W.t(), out=C)
+            done = cur.record_event()
+            in_free[b][li] = done
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                host_out[li].copy_(out, non_blocking=True)
+                out.record_stream(s_out)
+                leaving.append(s_out.record_event())
+        # this step's results have left the device before the next step may overwrite C or the host buffers
+        for ev in leaving:
+            cur.wait_event(ev)
     for i in range(3):
         e2e_step(i)
     ms_e2e = timed(e2e_step, max(3, args.steps // 2))
