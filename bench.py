@@ -149,14 +149,14 @@ def run_reference_arm(args):
     dt = (time.perf_counter() - t0) / args.steps
     val = step_flops(rows) / dt / 1e12
     sample = f"{rows} of {args.m} token rows of both layers per step, bf16, all host threads"
-    print(json.dumps({
+    _emit({
         "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args, args.gpus),
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }))
+    })
 
 
 def workload_config(args, n):
@@ -169,7 +169,31 @@ def workload_config(args, n):
 
 
 # --------------------------------------------------------------------------- GPU arm
+_RESULT_FD = None
+
+
+def _claim_stdout():
+    """Keep the process's stdout for the one JSON line: everything else that writes to file descriptor 1 from here
+    on (NCCL prints its version banner there) goes to stderr."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def _emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        sys.stdout.flush()
+        os.write(_RESULT_FD, data)
+
+
 def main():
+    _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
@@ -339,7 +363,7 @@ def main():
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
-        print(json.dumps(line))
+        _emit(line)
     if tp > 1:
         dist.destroy_process_group()
 
