@@ -14,6 +14,7 @@ sys.path.insert(0, os.path.join(HERE, "golden"))
 
 from make_golden import AR_CASES, MATMUL_CASES, ar_input, make_inputs  # noqa: E402
 from oracle.tbik_ref import (  # noqa: E402
+    exact_int_inputs,
     sharded_matmul_ref,
     tbik_matmul_ref,
     tree_allreduce_ref,
@@ -87,3 +88,53 @@ def test_batch_invariance_of_oracle():
     A, B = exact_int_inputs(32, 1536, 64, torch.bfloat16, seed=3)
     full = tbik_matmul_ref(A, B)
     assert torch.equal(bits(full[:7]), bits(tbik_matmul_ref(A[:7], B)))
+
+
+# ---------------------------------------------------------------- the C restatement (oracle/tbik_ref.c)
+INT_CASES = [c for c in MATMUL_CASES if c[5] == "int" and c[1] in (torch.float16, torch.bfloat16)]
+AR16_CASES = [c for c in AR_CASES if c[1] in (torch.float16, torch.bfloat16)]
+
+
+@pytest.mark.parametrize("case", INT_CASES, ids=[c[0] for c in INT_CASES])
+def test_c_oracle_matches_reference_kernel(case):
+    """Scalar C loops against the stored outputs of the reference's own kernel, every tree shape."""
+    from oracle import c_oracle
+    name, dt, M, K, N, gen, seed = case
+    A, B = make_inputs(dt, M, K, N, gen, seed)
+    assert torch.equal(bits(c_oracle.matmul(A, B)), bits(GOLD_MM[name]))
+
+
+@pytest.mark.parametrize("case", AR16_CASES, ids=[c[0] for c in AR16_CASES])
+def test_c_oracle_allreduce_matches_reference_native(case):
+    from oracle import c_oracle
+    name, dt, world, numel, seed = case
+    parts = [ar_input(dt, r, numel, seed) for r in range(world)]
+    assert torch.equal(bits(c_oracle.tree_allreduce(parts)), bits(GOLD_AR[name]))
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_c_oracle_conversions_are_round_to_nearest_even(dt):
+    """Its own 16-bit conversions against torch's: every bit pattern upwards; random values, every midpoint between
+    neighbouring representable values, overflow and underflow edges downwards."""
+    from oracle import c_oracle
+    allp = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(dt)
+    a, b = c_oracle.up(allp), allp.float()
+    assert bool(((a.view(torch.int32) == b.view(torch.int32)) | (a.isnan() & b.isnan())).all())
+    g = torch.Generator().manual_seed(0)
+    x = torch.cat([torch.randn(200_000, generator=g) * s for s in (1e-8, 1e-5, 1e-3, 1.0, 300.0, 7e4)])
+    mid = (b[:-1] + b[1:]) / 2
+    edges = torch.tensor([0.0, -0.0, float("inf"), -float("inf"), 65504.0, 65519.9, 65520.0, 65536.0,
+                          5.96e-8, 2.98e-8, 2.9802322e-8, 2.99e-8, 3.4e38, -3.4e38])
+    x = torch.cat([x, mid[torch.isfinite(mid)], edges])
+    assert torch.equal(bits(c_oracle.down(x, dt)), bits(x.to(dt)))
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,K,N", [(5, 256, 8), (7, 1536, 24), (3, 4096, 16), (4, 12288, 8), (2, 25600, 8), (9, 768, 40)])
+def test_c_and_python_oracles_agree(dt, M, K, N):
+    from oracle import c_oracle
+    A, B = exact_int_inputs(M, K, N, dt, seed=K + M, amax=7)
+    assert torch.equal(bits(c_oracle.matmul(A, B)), bits(tbik_matmul_ref(A, B)))
+    parts = [torch.randn(777, generator=torch.Generator().manual_seed(r)).to(dt) for r in range(8)]
+    for w in (1, 2, 4, 8):
+        assert torch.equal(bits(c_oracle.tree_allreduce(parts[:w])), bits(tree_allreduce_ref(parts[:w])))
