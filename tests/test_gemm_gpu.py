@@ -73,6 +73,16 @@ def test_bit_exact_vs_oracle_integer_operands(mm, dt, M, K, N):
     assert torch.equal(bits(C.cpu()), bits(tbik_matmul_ref(A, B)))
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,K,N", [(1, 4096, 64), (37, 1536, 200), (130, 12288, 136), (16, 25600, 128)])
+def test_bit_exact_vs_c_oracle_integer_operands(mm, dt, M, K, N):
+    """The CUDA path against the plain-C restatement (scalar loops, own conversions), decode- and prefill-sized."""
+    from oracle import c_oracle
+    A, B = exact_int_inputs(M, K, N, dt, seed=M + K + N, amax=7)
+    C = mm(A.cuda(), kmajor(B))
+    assert torch.equal(bits(C.cpu()), bits(c_oracle.matmul(A, B)))
+
+
 @pytest.mark.parametrize("K", [16384, 32768])
 def test_deep_trees_use_the_shared_memory_levels(mm, K):
     """L = 6 and 7: levels above the TMEM stack are kept in shared memory."""
