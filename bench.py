@@ -13,8 +13,10 @@ bitwise equal to the N = 1 result.
 Prints ONE JSON line (rank 0).  `value` is whole-job TFLOP/s = 2*M*4096*(4096+12288) / step time,
 device-timed with CUDA events, max over ranks.  `e2e` is the same metric through the public
 Python API with HOST activations: pinned host -> device copy of X, GEMM (+ all-reduce), device ->
-pinned host copy of the result, all inside the timed region (weights stay resident: they are
-parameters, not per-step inputs).  `roofline` is for the dominant kernel (the down_proj GEMM):
+pinned host copy of the result, all inside the timed region, every step (the copies run on two copy
+streams beside the compute stream with double-buffered device inputs, so step i+1's input copy
+overlaps step i's GEMMs and result copy; weights stay resident: they are parameters, not per-step
+inputs).  `roofline` is for the dominant kernel (the down_proj GEMM):
 algorithmic FLOPs per launch / mean launch duration measured live here, against the measured
 dense-bf16 peak in MEASURED_PEAKS.json.  `cpu_baseline` times the CPU oracle on a bounded sample.
 
