@@ -138,3 +138,21 @@ def test_c_and_python_oracles_agree(dt, M, K, N):
     parts = [torch.randn(777, generator=torch.Generator().manual_seed(r)).to(dt) for r in range(8)]
     for w in (1, 2, 4, 8):
         assert torch.equal(bits(c_oracle.tree_allreduce(parts[:w])), bits(tree_allreduce_ref(parts[:w])))
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("K,tps", [(4096, (2, 4, 8)), (12288, (2, 4, 8)), (6144, (2, 4, 8)), (25600, (2, 4))])
+def test_c_oracle_is_shard_invariant(dt, K, tps):
+    """The property the whole path exists for, stated on the C restatement alone: K-shards reduced separately and
+    combined by the rank-pair tree give the bits of the unsplit reduction (random operands, not integer ones)."""
+    from oracle import c_oracle
+    g = torch.Generator().manual_seed(K)
+    A = torch.randn(6, K, generator=g).to(dt)
+    B = (torch.randn(K, 24, generator=g) * 0.02).to(dt)
+    full = c_oracle.matmul(A, B)
+    for tp in tps:
+        ks = K // tp
+        parts = [c_oracle.matmul(A[:, r * ks:(r + 1) * ks], B[r * ks:(r + 1) * ks]) for r in range(tp)]
+        assert torch.equal(bits(c_oracle.tree_allreduce(parts)), bits(full)), tp
+    # batch invariance: a row computed alone has the bits it has inside the batch
+    assert torch.equal(bits(c_oracle.matmul(A[2:3], B)), bits(full[2:3]))
