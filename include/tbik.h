@@ -140,6 +140,9 @@ typedef void* tbik_ar_t;
 #define TBIK_AR_CFG_THREADS 5           /* threads per CTA, a multiple of 32 in [32, 512] (0 = built-in) */
 #define TBIK_AR_CFG_PUSH_MIN_BYTES 6    /* messages from this size on use the push schedule (0 = built-in, 1 = all two-shot sizes) */
 #define TBIK_AR_CFG_PUSH_CHUNKS 7       /* chunks the push schedule cuts a message into, 1..64 (0 = built-in) */
+#define TBIK_AR_CFG_VEC_PACKS 8         /* 16-byte packs per load / store instruction: 1, or 2 = 256-bit accesses (0 = built-in) */
+#define TBIK_AR_CFG_LOADS_IN_FLIGHT 9   /* 16-byte packs a thread requests before it uses the first, 1..32 (0 = built-in) */
+#define TBIK_AR_CFG_TRACE 10            /* 1: every launch records per-CTA phase time stamps (tbik_ar_trace); 0: off      */
 
 /* Size in bytes of the signal (flag) area at the start of every rank's meta buffer.
  * Replaces: meta_size, mini_allreduce/tbik_kernel/csrc/allreduce/custom_all_reduce.cu:148-150. */
@@ -174,6 +177,15 @@ int tbik_ar_register_buffer(tbik_ar_t comm, void* const* ptrs);
 int tbik_ar_tree_allreduce(tbik_ar_t comm, const void* inp, void* out, int64_t numel, int dtype, void* reg_buffer,
                            size_t reg_buffer_bytes, tbik_stream_t stream);
 
+/* Tree all-reduce of a message that a producer kernel wrote IN PLACE inside a registered buffer: the message is
+ * the numel elements that start byte_offset bytes into the buffer registered at reg_base (same offset on every
+ * rank; a multiple of 16).  No staging copy.  This is how the row-split layer overlaps its two halves: the GEMM
+ * writes row blocks of its partial result into the registered buffer, and each block is reduced, on a second
+ * stream, while the GEMM computes the next one.
+ * Replaces: the same reference functions as tbik_ar_tree_allreduce, minus the copy at custom_all_reduce.cu:112-114. */
+int tbik_ar_tree_allreduce_within(tbik_ar_t comm, const void* reg_base, size_t byte_offset, void* out, int64_t numel,
+                                  int dtype, tbik_stream_t stream);
+
 /* As above with the non-tree arithmetic: fp32 accumulation in rank order, one final rounding.
  * Replaces: all_reduce, custom_all_reduce.cu:57-98 / allreduce, custom_all_reduce.cuh:462-521. */
 int tbik_ar_allreduce(tbik_ar_t comm, const void* inp, void* out, int64_t numel, int dtype, void* reg_buffer,
@@ -192,6 +204,13 @@ int tbik_ar_register_graph_buffers(tbik_ar_t comm, const void* const* handles, c
  * out[0] 0 = healthy, 1 = a barrier wait ran out; out[1..6] = rank, block, peer, expected epoch,
  * value seen, barrier id.  No counterpart in the reference (custom_all_reduce.cuh:182,186 spin forever). */
 int tbik_ar_status(tbik_ar_t comm, uint32_t out[8]);
+
+/* Phase time stamps of the most recent all-reduce launch (needs TBIK_AR_CFG_TRACE = 1; synchronise the stream
+ * first): for each of its CTAs eight GPU-timer values in nanoseconds -- [0] kernel entry, [1] after the first
+ * cross-GPU barrier, [2] after the reduce phase, [3] after the middle barrier (two-shot only), [4] exit.  `out`
+ * has room for 8 * max_blocks values; *blocks receives the number of CTAs recorded.  This is how the phases of a
+ * multi-rank kernel are timed without a profiler.  No counterpart in the reference. */
+int tbik_ar_trace(tbik_ar_t comm, uint64_t* out, int max_blocks, int* blocks);
 
 /* The whole row-split layer in ONE kernel launch: out = tree-all-reduce over ranks of (A * W^T), with the
  * K reduction of every rank in the fixed tree order and the cross-rank levels in the rank-pair order --

@@ -40,6 +40,8 @@ _PROTOTYPES = {
     "tbik_ar_register_buffer": (_i32, [_vp, ctypes.POINTER(_vp)]),
     "tbik_ar_tree_allreduce": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp, _sz, _vp]),
     "tbik_ar_allreduce": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp, _sz, _vp]),
+    "tbik_ar_tree_allreduce_within": (_i32, [_vp, _vp, _sz, _vp, _i64, _i32, _vp]),
+    "tbik_ar_trace": (_i32, [_vp, ctypes.POINTER(ctypes.c_uint64), _i32, ctypes.POINTER(_i32)]),
     "tbik_ar_graph_meta_count": (_i32, [_vp, ctypes.POINTER(_i32)]),
     "tbik_ar_graph_meta": (_i32, [_vp, _vp, ctypes.POINTER(_i64)]),
     "tbik_ar_register_graph_buffers": (_i32, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(ctypes.POINTER(_i64))]),

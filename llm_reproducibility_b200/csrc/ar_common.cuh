@@ -10,7 +10,7 @@
 namespace tbik {
 
 constexpr int kMaxRanks = 8;
-constexpr int kMaxBlocks = 160;
+constexpr int kMaxBlocks = 320;  // up to two CTAs per SM
 
 constexpr int kMaxTiles = 8192;  // output tiles per fused GEMM + all-reduce call
 

@@ -106,6 +106,15 @@ int tbik_ar_allreduce(tbik_ar_t comm, const void* inp, void* out, int64_t numel,
                       static_cast<cudaStream_t>(stream));
 }
 
+int tbik_ar_tree_allreduce_within(tbik_ar_t comm, const void* reg_base, size_t byte_offset, void* out, int64_t numel,
+                                  int dtype, tbik_stream_t stream) {
+  return tbik::ar_run_within(comm, reg_base, byte_offset, out, numel, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int tbik_ar_trace(tbik_ar_t comm, uint64_t* out, int max_blocks, int* blocks) {
+  return tbik::ar_trace(comm, out, max_blocks, blocks);
+}
+
 int tbik_ar_graph_meta_count(tbik_ar_t comm, int* n) { return tbik::ar_graph_meta_count(comm, n); }
 
 int tbik_ar_graph_meta(tbik_ar_t comm, void* handles_out, int64_t* offsets_out) {

@@ -51,6 +51,9 @@ int ar_configure(tbik_ar_t h, int key, int64_t value);
 int ar_register_buffer(tbik_ar_t h, void* const* ptrs);
 int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, void* reg_buffer, size_t reg_bytes,
            bool tree, cudaStream_t stream);
+int ar_run_within(tbik_ar_t h, const void* reg_base, size_t byte_offset, void* out, int64_t numel, int dtype,
+                  cudaStream_t stream);
+int ar_trace(tbik_ar_t h, uint64_t* out, int max_blocks, int* blocks);
 int ar_graph_meta_count(tbik_ar_t h, int* n);
 int ar_graph_meta(tbik_ar_t h, void* handles_out, int64_t* offsets_out);
 int ar_register_graph_buffers(tbik_ar_t h, const void* const* handles, const int64_t* const* offsets);

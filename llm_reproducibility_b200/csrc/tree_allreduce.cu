@@ -33,6 +33,7 @@
 
 #include <map>
 #include <string>
+#include <type_traits>
 #include <unordered_map>
 #include <vector>
 
@@ -45,110 +46,200 @@ constexpr int kThreads = 512;
 constexpr uint64_t kArWaitLimitNs = 2000000000ull;  // default bound of one barrier wait
 constexpr size_t kPushMinBytesDefault = ~size_t(0);   // push schedule: only when configured
 
-// One 16-byte pack reduced over the NG ranks.  TREE: rank-pair tree in T; else rank order in fp32.
-template <typename T, int NG, bool TREE>
-__device__ __forceinline__ uint4 reduce_pack(const RankData& dp, int64_t idx) {
-  uint4 v[NG];
-#pragma unroll
-  for (int r = 0; r < NG; ++r) v[r] = ld_pack(reinterpret_cast<const uint4*>(dp.ptrs[r]) + idx);
-  if constexpr (TREE) {
-#pragma unroll
-    for (int stride = 1; stride < NG; stride *= 2) {
-#pragma unroll
-      for (int i = 0; i + stride < NG; i += 2 * stride) v[i] = Elem<T>::add(v[i], v[i + stride]);
-    }
-    return v[0];
+// A vector is VEC consecutive 16-byte packs moved by one load / store instruction (VEC = 2: 256-bit accesses).
+template <int VEC>
+struct Vec {
+  uint4 q[VEC];
+};
+
+template <int VEC>
+__device__ __forceinline__ Vec<VEC> ld_vec(const void* base, int64_t vidx) {
+  Vec<VEC> v;
+  if constexpr (VEC == 1) {
+    v.q[0] = ld_pack(reinterpret_cast<const uint4*>(base) + vidx);
   } else {
-    float acc[8], t[8];
-    Elem<T>::up(v[0], acc);
+    static_assert(VEC == 2, "vectors are 16 or 32 bytes");
+    const void* p = reinterpret_cast<const char*>(base) + vidx * 32;
+    asm volatile("ld.relaxed.sys.global.v8.u32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v.q[0].x), "=r"(v.q[0].y), "=r"(v.q[0].z), "=r"(v.q[0].w), "=r"(v.q[1].x), "=r"(v.q[1].y),
+                   "=r"(v.q[1].z), "=r"(v.q[1].w)
+                 : "l"(p)
+                 : "memory");
+  }
+  return v;
+}
+
+template <int VEC>
+__device__ __forceinline__ void st_vec(void* base, int64_t vidx, const Vec<VEC>& v) {
+  if constexpr (VEC == 1) {
+    reinterpret_cast<uint4*>(base)[vidx] = v.q[0];
+  } else {
+    void* p = reinterpret_cast<char*>(base) + vidx * 32;
+    asm volatile("st.global.v8.u32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};" ::"r"(v.q[0].x), "r"(v.q[0].y),
+                 "r"(v.q[0].z), "r"(v.q[0].w), "r"(v.q[1].x), "r"(v.q[1].y), "r"(v.q[1].z), "r"(v.q[1].w), "l"(p)
+                 : "memory");
+  }
+}
+
+// NG vectors, one per rank, combined.  TREE: rank-pair tree in T; else rank order in fp32.
+template <typename T, int NG, bool TREE, int VEC>
+__device__ __forceinline__ Vec<VEC> combine(Vec<VEC> (&v)[NG]) {
 #pragma unroll
-    for (int r = 1; r < NG; ++r) {
-      Elem<T>::up(v[r], t);
+  for (int j = 0; j < VEC; ++j) {
+    if constexpr (TREE) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] += t[i];
+      for (int stride = 1; stride < NG; stride *= 2) {
+#pragma unroll
+        for (int i = 0; i + stride < NG; i += 2 * stride) v[i].q[j] = Elem<T>::add(v[i].q[j], v[i + stride].q[j]);
+      }
+    } else {
+      float acc[8], t[8];
+      Elem<T>::up(v[0].q[j], acc);
+#pragma unroll
+      for (int r = 1; r < NG; ++r) {
+        Elem<T>::up(v[r].q[j], t);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += t[i];
+      }
+      v[0].q[j] = Elem<T>::down(acc);
     }
-    return Elem<T>::down(acc);
+  }
+  return v[0];
+}
+
+// What every schedule's kernel gets.  Sizes are in vectors of VEC packs.
+struct ArArgs {
+  const RankData* dp;  // every rank's address of the registered buffer the message lives in
+  RankSignals sg;
+  Signal* self;
+  void* out;
+  int64_t nvec;     // length of the message
+  int64_t in_off;   // where the message starts inside the registered buffer
+  ArStatus* status;
+  uint64_t limit_ns;
+  uint64_t* trace;  // optional (host-mapped): [block][8] globaltimer stamps of the phases of the last launch
+  int rank;
+  int chunks;       // push schedule only
+};
+
+__device__ __forceinline__ void stamp(const ArArgs& a, int slot) {
+  if (a.trace != nullptr && threadIdx.x == 0) a.trace[blockIdx.x * 8 + slot] = ar_timer_ns();
+}
+
+// Reduce vectors [lo, hi) of the message (indices relative to its start) and hand each result to `sink(i, v)`.
+// UNROLL vectors per thread are in flight at once: all UNROLL * NG loads are issued before the first add.
+template <typename T, int NG, bool TREE, int VEC, int UNROLL, typename Sink>
+__device__ __forceinline__ void reduce_range(const RankData& dp, int64_t in_off, int64_t lo, int64_t hi, int64_t tid,
+                                             int64_t stride, Sink sink) {
+  int64_t idx = lo + tid;
+  for (; idx + (UNROLL - 1) * stride < hi; idx += UNROLL * stride) {
+    Vec<VEC> v[UNROLL][NG];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+      for (int r = 0; r < NG; ++r) v[u][r] = ld_vec<VEC>(dp.ptrs[r], in_off + idx + u * stride);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) sink(idx + u * stride, combine<T, NG, TREE, VEC>(v[u]));
+  }
+  for (; idx < hi; idx += stride) {
+    Vec<VEC> v[NG];
+#pragma unroll
+    for (int r = 0; r < NG; ++r) v[r] = ld_vec<VEC>(dp.ptrs[r], in_off + idx);
+    sink(idx, combine<T, NG, TREE, VEC>(v));
   }
 }
 
-template <typename T, int NG, bool TREE>
-__global__ void __launch_bounds__(kThreads, 1)
-allreduce_oneshot_kernel(const RankData* dp_ptr, RankSignals sg, Signal* self, void* out, int rank, int64_t npacks,
-                         ArStatus* status, uint64_t limit_ns) {
+template <typename T, int NG, bool TREE, int VEC, int UNROLL>
+__global__ void __launch_bounds__(kThreads, 1) allreduce_oneshot_kernel(const ArArgs a) {
   __shared__ uint32_t fail;
   if (threadIdx.x == 0) fail = 0u;
-  const RankData dp = *dp_ptr;
-  if (!block_barrier<NG>(sg, self, rank, status, limit_ns, 1, &fail)) return;
-  uint4* o = reinterpret_cast<uint4*>(out);
+  stamp(a, 0);
+  const RankData dp = *a.dp;
+  if (!block_barrier<NG>(a.sg, a.self, a.rank, a.status, a.limit_ns, 1, &fail)) return;
+  stamp(a, 1);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  // kUnroll independent packs per thread keep kUnroll * NG 16-byte peer loads in flight
-  constexpr int kUnroll = NG >= 8 ? 2 : 4;
-  for (; idx + (kUnroll - 1) * stride < npacks; idx += kUnroll * stride) {
-    uint4 r[kUnroll];
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) r[u] = reduce_pack<T, NG, TREE>(dp, idx + u * stride);
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) o[idx + u * stride] = r[u];
-  }
-  for (; idx < npacks; idx += stride) o[idx] = reduce_pack<T, NG, TREE>(dp, idx);
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  void* out = a.out;
+  reduce_range<T, NG, TREE, VEC, UNROLL>(dp, a.in_off, 0, a.nvec, tid, stride,
+                                         [&](int64_t i, const Vec<VEC>& v) { st_vec<VEC>(out, i, v); });
+  stamp(a, 2);
   // peers may still be reading this rank's buffer: nobody leaves before everybody is done
-  block_barrier<NG>(sg, self, rank, status, limit_ns, 3, &fail);
+  block_barrier<NG>(a.sg, a.self, a.rank, a.status, a.limit_ns, 3, &fail);
+  stamp(a, 4);
 }
 
-template <typename T, int NG, bool TREE>
-__global__ void __launch_bounds__(kThreads, 1)
-allreduce_twoshot_kernel(const RankData* dp_ptr, RankSignals sg, Signal* self, void* out, int rank, int64_t npacks,
-                         ArStatus* status, uint64_t limit_ns) {
+template <typename T, int NG, bool TREE, int VEC, int UNROLL>
+__global__ void __launch_bounds__(kThreads, 1) allreduce_twoshot_kernel(const ArArgs a) {
   __shared__ uint32_t fail;
   if (threadIdx.x == 0) fail = 0u;
-  const RankData dp = *dp_ptr;
-  const int64_t part = npacks / NG;
+  stamp(a, 0);
+  const RankData dp = *a.dp;
+  const int rank = a.rank;
+  const int64_t part = a.nvec / NG;
   const int64_t start = rank * part;
-  const int64_t end = rank == NG - 1 ? npacks : start + part;
+  const int64_t end = rank == NG - 1 ? a.nvec : start + part;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  uint4* scratch[NG];
+  void* scratch[NG];
 #pragma unroll
-  for (int r = 0; r < NG; ++r) scratch[r] = reinterpret_cast<uint4*>(sg.sig[r] + 1);
+  for (int r = 0; r < NG; ++r) scratch[r] = a.sg.sig[r] + 1;
 
-  if (!block_barrier<NG>(sg, self, rank, status, limit_ns, 1, &fail)) return;
-  // reduce-scatter: this rank owns packs [start, end)
+  if (!block_barrier<NG>(a.sg, a.self, rank, a.status, a.limit_ns, 1, &fail)) return;
+  stamp(a, 1);
+  // reduce-scatter: this rank owns vectors [start, end)
   {
-    constexpr int kUnroll = NG >= 8 ? 2 : 4;
-    int64_t idx = start + tid;
-    for (; idx + (kUnroll - 1) * stride < end; idx += kUnroll * stride) {
-      uint4 r[kUnroll];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) r[u] = reduce_pack<T, NG, TREE>(dp, idx + u * stride);
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) scratch[rank][idx + u * stride - start] = r[u];
-    }
-    for (; idx < end; idx += stride) scratch[rank][idx - start] = reduce_pack<T, NG, TREE>(dp, idx);
+    void* mine = scratch[rank];
+    reduce_range<T, NG, TREE, VEC, UNROLL>(dp, a.in_off, start, end, tid, stride,
+                                           [&](int64_t i, const Vec<VEC>& v) { st_vec<VEC>(mine, i - start, v); });
   }
+  stamp(a, 2);
   // release this rank's scratch writes / acquire the peers'
-  if (!block_barrier<NG>(sg, self, rank, status, limit_ns, 2, &fail)) return;
-  // all-gather: same thread <-> same pack offset in both phases
-  uint4* o = reinterpret_cast<uint4*>(out);
-  const int64_t largest = part + npacks % NG;
-  for (int64_t idx = tid; idx < largest; idx += stride) {
+  if (!block_barrier<NG>(a.sg, a.self, rank, a.status, a.limit_ns, 2, &fail)) return;
+  stamp(a, 3);
+  // all-gather: same thread <-> same offset in both phases.  All NG loads of an offset (two offsets when the
+  // message is long enough) are in flight before the first store: a load answered over NVLink takes
+  // microseconds, and a thread that stored each vector before asking for the next one would move 16 bytes
+  // per round trip.
+  void* out = a.out;
+  const int64_t last = a.nvec - part * (NG - 1);  // length of the last rank's part (>= part)
+  constexpr int GU = (NG >= 8 ? 2 : 4) / VEC;  // offsets per thread in flight: 16 packs of payload
+  int64_t idx = tid;
+  for (; idx + (GU - 1) * stride < part; idx += GU * stride) {
+    Vec<VEC> v[GU][NG];
 #pragma unroll
-    for (int src = 0; src < NG; ++src) {
-      if (src == NG - 1 || idx < part) o[src * part + idx] = ld_pack(scratch[src] + idx);
+    for (int u = 0; u < GU; ++u) {
+#pragma unroll
+      for (int src = 0; src < NG; ++src) v[u][src] = ld_vec<VEC>(scratch[src], idx + u * stride);
+    }
+#pragma unroll
+    for (int u = 0; u < GU; ++u) {
+#pragma unroll
+      for (int src = 0; src < NG; ++src) st_vec<VEC>(out, src * part + idx + u * stride, v[u][src]);
     }
   }
+  for (; idx < last; idx += stride) {
+    Vec<VEC> v[NG];
+#pragma unroll
+    for (int src = 0; src < NG; ++src)
+      if (src == NG - 1 || idx < part) v[src] = ld_vec<VEC>(scratch[src], idx);
+#pragma unroll
+    for (int src = 0; src < NG; ++src)
+      if (src == NG - 1 || idx < part) st_vec<VEC>(out, src * part + idx, v[src]);
+  }
+  stamp(a, 4);
 }
 
-// Push schedule.  Every rank owns the r-th 1/n of the packs, cut into `chunks` chunks; every block works on the
+// Push schedule.  Every rank owns the r-th 1/n of the vectors, cut into `chunks` chunks; every block works on the
 // same index set of every (chunk, part) on every rank, so block b of rank p only ever depends on block b of
 // the other ranks.  No barrier after the first one: by the time a rank has seen all its flags, every peer has
 // finished reading this rank's input and writing this rank's scratch.
-template <typename T, int NG, bool TREE>
-__global__ void __launch_bounds__(kThreads, 1)
-allreduce_push_kernel(const RankData* dp_ptr, RankSignals sg, Signal* self, void* out, int rank, int64_t npacks,
-                      ArStatus* status, uint64_t limit_ns, int chunks) {
+template <typename T, int NG, bool TREE, int VEC, int UNROLL>
+__global__ void __launch_bounds__(kThreads, 1) allreduce_push_kernel(const ArArgs a) {
   __shared__ uint32_t fail;
   __shared__ uint32_t base_s;
+  const int rank = a.rank;
+  Signal* self = a.self;
   if (threadIdx.x == 0) {
     fail = 0u;
     // call counter kept on the device so that a captured graph advances it on every replay
@@ -156,17 +247,20 @@ allreduce_push_kernel(const RankData* dp_ptr, RankSignals sg, Signal* self, void
     self->push_calls[blockIdx.x] = k;
     base_s = k << 12;
   }
-  const RankData dp = *dp_ptr;
-  uint4* scratch[NG];
+  stamp(a, 0);
+  const RankData dp = *a.dp;
+  void* scratch[NG];
 #pragma unroll
-  for (int r = 0; r < NG; ++r) scratch[r] = reinterpret_cast<uint4*>(sg.sig[r] + 1);
+  for (int r = 0; r < NG; ++r) scratch[r] = a.sg.sig[r] + 1;
   // every rank has entered this call: inputs are final, nobody still reads last call's scratch
-  if (!block_barrier<NG>(sg, self, rank, status, limit_ns, 1, &fail)) return;
+  if (!block_barrier<NG>(a.sg, self, rank, a.status, a.limit_ns, 1, &fail)) return;
+  stamp(a, 1);
   const uint32_t base = base_s;
-  const int64_t part = npacks / NG;
-  const int64_t last_len = npacks - part * (NG - 1);
+  const int chunks = a.chunks;
+  const int64_t part = a.nvec / NG;
+  const int64_t last_len = a.nvec - part * (NG - 1);
   const int64_t clen = (last_len + chunks - 1) / chunks;
-  uint4* o = reinterpret_cast<uint4*>(out);
+  void* out = a.out;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   const int64_t my_len = rank == NG - 1 ? last_len : part;
@@ -176,48 +270,39 @@ allreduce_push_kernel(const RankData* dp_ptr, RankSignals sg, Signal* self, void
     const int64_t lo = c * clen;
     int64_t hi = lo + clen;
     if (hi > my_len) hi = my_len;
-    constexpr int kUnroll = 2;
-    int64_t idx = lo + tid;
-    for (; idx + (kUnroll - 1) * stride < hi; idx += kUnroll * stride) {
-      uint4 v[kUnroll];
+    reduce_range<T, NG, TREE, VEC, UNROLL>(dp, a.in_off, my_start + lo, my_start + hi, tid, stride,
+                                           [&](int64_t i, const Vec<VEC>& v) {
+                                             st_vec<VEC>(out, i, v);
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) v[u] = reduce_pack<T, NG, TREE>(dp, my_start + idx + u * stride);
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        o[my_start + idx + u * stride] = v[u];
-#pragma unroll
-        for (int p = 0; p < NG; ++p)
-          if (p != rank) scratch[p][my_start + idx + u * stride] = v[u];
-      }
-    }
-    for (; idx < hi; idx += stride) {
-      const uint4 v = reduce_pack<T, NG, TREE>(dp, my_start + idx);
-      o[my_start + idx] = v;
-#pragma unroll
-      for (int p = 0; p < NG; ++p)
-        if (p != rank) scratch[p][my_start + idx] = v;
-    }
+                                             for (int p = 0; p < NG; ++p)
+                                               if (p != rank) st_vec<VEC>(scratch[p], i, v);
+                                           });
     __syncthreads();  // the block's stores are ordered before the releases below
     if (threadIdx.x < NG && static_cast<int>(threadIdx.x) != rank)
-      st_flag_release(&sg.sig[threadIdx.x]->push_flag[blockIdx.x][rank], base + static_cast<uint32_t>(c) + 1u);
+      st_flag_release(&a.sg.sig[threadIdx.x]->push_flag[blockIdx.x][rank], base + static_cast<uint32_t>(c) + 1u);
   };
   auto gather_chunk = [&](int c) -> bool {
     if (threadIdx.x < NG && static_cast<int>(threadIdx.x) != rank) {
-      if (!wait_flag_reached(&self->push_flag[blockIdx.x][threadIdx.x], base + static_cast<uint32_t>(c) + 1u, status,
-                             limit_ns, rank, threadIdx.x, 4))
+      if (!wait_flag_reached(&self->push_flag[blockIdx.x][threadIdx.x], base + static_cast<uint32_t>(c) + 1u, a.status,
+                             a.limit_ns, rank, threadIdx.x, 4))
         fail = 1u;
     }
     __syncthreads();
     if (fail != 0u) return false;
     const int64_t lo = c * clen;
+    // local copy scratch -> result; the loads of all sources are issued before the stores
+    for (int64_t idx = lo + tid; idx < lo + clen; idx += stride) {
+      Vec<VEC> v[NG];
 #pragma unroll
-    for (int src = 0; src < NG; ++src) {
-      if (src == rank) continue;
-      int64_t hi = lo + clen;
-      const int64_t len = src == NG - 1 ? last_len : part;
-      if (hi > len) hi = len;
-      const int64_t start = src * part;
-      for (int64_t idx = lo + tid; idx < hi; idx += stride) o[start + idx] = ld_pack(scratch[rank] + start + idx);
+      for (int src = 0; src < NG; ++src) {
+        const int64_t len = src == NG - 1 ? last_len : part;
+        if (src != rank && idx < len) v[src] = ld_vec<VEC>(scratch[rank], src * part + idx);
+      }
+#pragma unroll
+      for (int src = 0; src < NG; ++src) {
+        const int64_t len = src == NG - 1 ? last_len : part;
+        if (src != rank && idx < len) st_vec<VEC>(out, src * part + idx, v[src]);
+      }
     }
     return true;
   };
@@ -225,7 +310,9 @@ allreduce_push_kernel(const RankData* dp_ptr, RankSignals sg, Signal* self, void
     reduce_chunk(c);
     if (c >= 1 && !gather_chunk(c - 1)) return;
   }
+  stamp(a, 2);
   gather_chunk(chunks - 1);
+  stamp(a, 4);
 }
 
 // ==================================================================== host object
@@ -256,50 +343,96 @@ struct Communicator {
   ArStatus* status_dev = nullptr;
   int sm_count = 0;
   bool poisoned = false;
+  int vec_packs = 0;             // 0 / 1 = 128-bit accesses, 2 = 256-bit
+  int loads_in_flight = 0;       // 0 = built-in policy
+  uint64_t* trace_host = nullptr;  // phase stamps of the last launch (host-mapped), when tracing is on
+  uint64_t* trace_dev = nullptr;
+  int trace_blocks = 0;
   uint32_t tile_epoch = 0;  // fused GEMM + all-reduce calls made so far (same on every rank)
 };
 
 static Communicator* as_comm(tbik_ar_t h) { return reinterpret_cast<Communicator*>(h); }
 
-template <typename T, int NG, bool TREE>
-static int launch_ar(Communicator* c, const RankData* slot, void* out, int64_t npacks, bool twoshot, int blocks,
-                     int threads, cudaStream_t stream, int push_chunks = 0) {
-  if (push_chunks > 0) {
-    if constexpr (NG >= 2)
-      allreduce_push_kernel<T, NG, TREE><<<blocks, threads, 0, stream>>>(slot, c->sg, c->self, out, c->rank, npacks,
-                                                                          c->status_dev, c->wait_limit_ns, push_chunks);
-  } else if (twoshot)
-    allreduce_twoshot_kernel<T, NG, TREE><<<blocks, threads, 0, stream>>>(slot, c->sg, c->self, out, c->rank, npacks,
-                                                                            c->status_dev, c->wait_limit_ns);
-  else
-    allreduce_oneshot_kernel<T, NG, TREE><<<blocks, threads, 0, stream>>>(slot, c->sg, c->self, out, c->rank, npacks,
-                                                                            c->status_dev, c->wait_limit_ns);
+enum Schedule { kOneShot = 0, kTwoShot = 1, kPush = 2 };
+
+template <typename T, int NG, bool TREE, int VEC, int UNROLL>
+static int launch_kernel(const ArArgs& a, int sched, int blocks, int threads, cudaStream_t stream) {
+  if (sched == kPush) {
+    if constexpr (NG >= 2) allreduce_push_kernel<T, NG, TREE, VEC, UNROLL><<<blocks, threads, 0, stream>>>(a);
+  } else if (sched == kTwoShot) {
+    allreduce_twoshot_kernel<T, NG, TREE, VEC, UNROLL><<<blocks, threads, 0, stream>>>(a);
+  } else {
+    allreduce_oneshot_kernel<T, NG, TREE, VEC, UNROLL><<<blocks, threads, 0, stream>>>(a);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_cuda_error(e, "all-reduce kernel launch");
   return TBIK_OK;
 }
 
+// `vec` = 16-byte packs per load instruction (1 or 2), `loads` = 16-byte packs a thread keeps in flight (0 = the
+// built-in 16 for 4 and 8 ranks, 8 for 2).  The tuned variants exist for the path the row-split layer uses (bf16,
+// tree order); everything else runs the built-in shape.
+template <typename T, int NG, bool TREE>
+static int launch_ar(const ArArgs& a, int sched, int blocks, int threads, cudaStream_t stream, int vec, int loads) {
+  constexpr int kDefaultUnroll = NG >= 6 ? 2 : 4;
+  if constexpr (std::is_same<T, __nv_bfloat16>::value && TREE && NG >= 2) {
+    int unroll = loads > 0 ? loads / (NG * vec) : kDefaultUnroll / vec;
+    if (unroll < 1) unroll = 1;
+    while (unroll * NG * vec > 32) unroll /= 2;  // at most 32 packs = 128 registers of payload per thread
+    if (vec == 2) {
+      switch (unroll) {
+        case 1: return launch_kernel<T, NG, TREE, 2, 1>(a, sched, blocks, threads, stream);
+        case 2: return launch_kernel<T, NG, TREE, 2, 2>(a, sched, blocks, threads, stream);
+        case 4:
+          if constexpr (NG <= 4) return launch_kernel<T, NG, TREE, 2, 4>(a, sched, blocks, threads, stream);
+          break;
+        case 8:
+          if constexpr (NG <= 2) return launch_kernel<T, NG, TREE, 2, 8>(a, sched, blocks, threads, stream);
+          break;
+        default: break;
+      }
+      return launch_kernel<T, NG, TREE, 2, 1>(a, sched, blocks, threads, stream);
+    }
+    switch (unroll) {
+      case 1: return launch_kernel<T, NG, TREE, 1, 1>(a, sched, blocks, threads, stream);
+      case 2: return launch_kernel<T, NG, TREE, 1, 2>(a, sched, blocks, threads, stream);
+      case 4: return launch_kernel<T, NG, TREE, 1, 4>(a, sched, blocks, threads, stream);
+      case 8:
+        if constexpr (NG <= 4) return launch_kernel<T, NG, TREE, 1, 8>(a, sched, blocks, threads, stream);
+        break;
+      case 16:
+        if constexpr (NG <= 2) return launch_kernel<T, NG, TREE, 1, 16>(a, sched, blocks, threads, stream);
+        break;
+      default: break;
+    }
+  }
+  return launch_kernel<T, NG, TREE, 1, kDefaultUnroll>(a, sched, blocks, threads, stream);
+}
+
 template <typename T, bool TREE>
-static int dispatch_world(Communicator* c, const RankData* slot, void* out, int64_t npacks, bool twoshot, int blocks,
-                          int threads, cudaStream_t stream, int push_chunks) {
-  switch (c->world) {
+static int dispatch_world(int world, const ArArgs& a, int sched, int blocks, int threads, cudaStream_t stream, int vec,
+                          int loads) {
+  switch (world) {
     case 1:
-      if constexpr (TREE) return launch_ar<T, 1, TREE>(c, slot, out, npacks, false, blocks, threads, stream);
+      if constexpr (TREE) return launch_ar<T, 1, TREE>(a, kOneShot, blocks, threads, stream, 1, 0);
       break;
-    case 2: return launch_ar<T, 2, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks);
-    case 4: return launch_ar<T, 4, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks);
+    case 2: return launch_ar<T, 2, TREE>(a, sched, blocks, threads, stream, vec, loads);
+    case 4: return launch_ar<T, 4, TREE>(a, sched, blocks, threads, stream, vec, loads);
     case 6:
-      if constexpr (!TREE) return launch_ar<T, 6, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks);
+      if constexpr (!TREE) return launch_ar<T, 6, TREE>(a, sched, blocks, threads, stream, vec, loads);
       break;
-    case 8: return launch_ar<T, 8, TREE>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks);
+    case 8: return launch_ar<T, 8, TREE>(a, sched, blocks, threads, stream, vec, loads);
     default: break;
   }
   return set_error(TBIK_ERR_SHAPE, TREE ? "tree all-reduce supports 1, 2, 4 or 8 ranks"
                                         : "all-reduce supports 2, 4, 6 or 8 ranks");
 }
 
-int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, void* reg_buffer, size_t reg_bytes,
-           bool tree, cudaStream_t stream) {
+// `inp`: the message.  With `reg_buffer` it is first copied there; with `reg_base` it is a byte range inside the
+// registered buffer that starts at reg_base (a producer wrote it in place); else it must itself be registered
+// (or the stream is capturing).
+static int ar_run_impl(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, void* reg_buffer,
+                       size_t reg_bytes, const void* reg_base, bool tree, cudaStream_t stream) {
   Communicator* c = as_comm(h);
   if (!c) return set_error(TBIK_ERR_ARG, "all-reduce: null communicator");
   if (c->status_host && c->status_host->w[0] != 0) c->poisoned = true;
@@ -324,26 +457,32 @@ int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, vo
     src = reg_buffer;
   }
   if ((reinterpret_cast<uintptr_t>(src) & 15u) != 0) return set_error(TBIK_ERR_ALIGN, "all-reduce: input must be 16-byte aligned");
+  size_t byte_off = 0;
+  if (reg_base) {
+    if (reinterpret_cast<uintptr_t>(src) < reinterpret_cast<uintptr_t>(reg_base))
+      return set_error(TBIK_ERR_ARG, "all-reduce: the message lies before the registered buffer it was said to be in");
+    byte_off = reinterpret_cast<uintptr_t>(src) - reinterpret_cast<uintptr_t>(reg_base);
+    src = reg_base;
+  }
 
   // Which slot of the device table describes this buffer on every rank?
   const RankData* slot = nullptr;
   cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
   cudaError_t e = cudaStreamIsCapturing(stream, &cap);
   if (e != cudaSuccess) return set_cuda_error(e, "cudaStreamIsCapturing");
-  if (cap == cudaStreamCaptureStatusActive) {
+  auto it = c->registered.find(src);
+  if (it != c->registered.end()) {
+    slot = it->second;  // registered before: usable eagerly and under capture alike
+  } else if (cap == cudaStreamCaptureStatusActive) {
     // Peer addresses are unknown until the handles are exchanged after capture: reserve the slot now.
     if (c->rd_next + c->graph_pending.size() + 1 > c->rd_end)
       return set_error(TBIK_ERR_STATE, "all-reduce: rank-data table is full");
     slot = c->rd_next + c->graph_pending.size();
     c->graph_pending.push_back(const_cast<void*>(src));
   } else {
-    auto it = c->registered.find(src);
-    if (it == c->registered.end()) {
-      char msg[128];
-      snprintf(msg, sizeof(msg), "buffer address %llu is not registered!", (unsigned long long)reinterpret_cast<uintptr_t>(src));
-      return set_error(TBIK_ERR_STATE, msg);
-    }
-    slot = it->second;
+    char msg[128];
+    snprintf(msg, sizeof(msg), "buffer address %llu is not registered!", (unsigned long long)reinterpret_cast<uintptr_t>(src));
+    return set_error(TBIK_ERR_STATE, msg);
   }
 
   const int64_t npacks = static_cast<int64_t>(bytes / 16);
@@ -353,7 +492,7 @@ int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, vo
   if (one_max == 0) one_max = c->world <= 2 ? ~size_t(0) : (1u << 20);
   bool twoshot = c->world > 1 && bytes > one_max && c->full_nvlink;
   if (twoshot) {
-    const int64_t part = npacks / c->world + npacks % c->world;
+    const int64_t part = npacks / c->world + 2 * c->world;  // the last rank's part, in packs, rounded up
     if (static_cast<size_t>(part) * 16 > c->scratch_bytes) {
       if (bytes <= (8u << 20)) twoshot = false;  // small enough for the one-shot schedule
       else return set_error(TBIK_ERR_SHAPE, "all-reduce: message needs more scratch than the meta buffer provides (raise max_size)");
@@ -365,27 +504,62 @@ int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, vo
     const size_t push_min = c->push_min_bytes != 0 ? c->push_min_bytes : kPushMinBytesDefault;
     if (twoshot && bytes >= push_min && bytes <= c->scratch_bytes) {
       push_chunks = c->push_chunks > 0 ? c->push_chunks : 4;
-      const int64_t part = npacks / c->world;
+      const int64_t part = npacks / (2 * c->world);
       if (push_chunks > part) push_chunks = part > 0 ? static_cast<int>(part) : 1;
     }
   }
-  const int64_t work = twoshot ? (npacks + c->world - 1) / c->world : npacks;
+  // 256-bit accesses when asked for and every address involved is 32-byte aligned
+  int vec = c->vec_packs == 2 ? 2 : 1;
+  if (vec == 2 && (npacks % 2 != 0 || byte_off % 32 != 0 || (reinterpret_cast<uintptr_t>(out) & 31u) != 0 ||
+                   (reinterpret_cast<uintptr_t>(src) & 31u) != 0))
+    vec = 1;
+  const int64_t nvec = npacks / vec;
+  const int64_t work = twoshot ? (nvec + c->world - 1) / c->world : nvec;
   int cap_blocks = c->max_blocks > 0 ? c->max_blocks : (bytes <= (256u << 10) ? 36 : c->sm_count);
   if (cap_blocks > kMaxBlocks) cap_blocks = kMaxBlocks;
-  if (cap_blocks > c->sm_count) cap_blocks = c->sm_count;
   const int threads = c->threads > 0 ? c->threads : kThreads;
+  // every block of a launch must be resident at once (block b waits for block b of the peers)
+  const int resident = c->sm_count * (threads <= 256 ? 2 : 1);
+  if (cap_blocks > resident) cap_blocks = resident;
   int blocks = static_cast<int>((work + threads - 1) / threads);
   if (blocks > cap_blocks) blocks = cap_blocks;
   if (blocks < 1) blocks = 1;
 
+  ArArgs a{};
+  a.dp = slot;
+  a.sg = c->sg;
+  a.self = c->self;
+  a.out = out;
+  a.nvec = nvec;
+  a.in_off = static_cast<int64_t>(byte_off / (16 * vec));
+  a.status = c->status_dev;
+  a.limit_ns = c->wait_limit_ns;
+  a.trace = c->trace_dev;
+  a.rank = c->rank;
+  a.chunks = push_chunks;
+  if (c->trace_host) c->trace_blocks = blocks;
+  const int sched = push_chunks > 0 ? kPush : (twoshot ? kTwoShot : kOneShot);
+  const int loads = c->loads_in_flight;
   if (dtype == TBIK_DTYPE_FP32)
-    return tree ? dispatch_world<float, true>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks)
-                : dispatch_world<float, false>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks);
+    return tree ? dispatch_world<float, true>(c->world, a, sched, blocks, threads, stream, vec, loads)
+                : dispatch_world<float, false>(c->world, a, sched, blocks, threads, stream, vec, loads);
   if (dtype == TBIK_DTYPE_FP16)
-    return tree ? dispatch_world<__half, true>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks)
-                : dispatch_world<__half, false>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks);
-  return tree ? dispatch_world<__nv_bfloat16, true>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks)
-              : dispatch_world<__nv_bfloat16, false>(c, slot, out, npacks, twoshot, blocks, threads, stream, push_chunks);
+    return tree ? dispatch_world<__half, true>(c->world, a, sched, blocks, threads, stream, vec, loads)
+                : dispatch_world<__half, false>(c->world, a, sched, blocks, threads, stream, vec, loads);
+  return tree ? dispatch_world<__nv_bfloat16, true>(c->world, a, sched, blocks, threads, stream, vec, loads)
+              : dispatch_world<__nv_bfloat16, false>(c->world, a, sched, blocks, threads, stream, vec, loads);
+}
+
+int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, void* reg_buffer, size_t reg_bytes,
+           bool tree, cudaStream_t stream) {
+  return ar_run_impl(h, inp, out, numel, dtype, reg_buffer, reg_bytes, nullptr, tree, stream);
+}
+
+int ar_run_within(tbik_ar_t h, const void* reg_base, size_t byte_offset, void* out, int64_t numel, int dtype,
+                  cudaStream_t stream) {
+  if (!reg_base) return set_error(TBIK_ERR_ARG, "all-reduce: null registered buffer");
+  return ar_run_impl(h, static_cast<const char*>(reg_base) + byte_offset, out, numel, dtype, nullptr, 0, reg_base, true,
+                     stream);
 }
 
 int ar_gemm_tree_allreduce(tbik_ar_t h, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
@@ -468,6 +642,7 @@ int ar_destroy(tbik_ar_t h) {
   if (!c) return TBIK_OK;
   for (auto& kv : c->opened) cudaIpcCloseMemHandle(kv.second);
   if (c->status_host) cudaFreeHost(c->status_host);
+  if (c->trace_host) cudaFreeHost(c->trace_host);
   delete c;
   return TBIK_OK;
 }
@@ -484,6 +659,26 @@ int ar_configure(tbik_ar_t h, int key, int64_t value) {
     case TBIK_AR_CFG_PUSH_CHUNKS:
       if (value < 0 || value > 64) return set_error(TBIK_ERR_ARG, "tbik_ar_configure: push chunks must be 0..64");
       c->push_chunks = static_cast<int>(value);
+      return TBIK_OK;
+    case TBIK_AR_CFG_VEC_PACKS:
+      if (value != 0 && value != 1 && value != 2) return set_error(TBIK_ERR_ARG, "tbik_ar_configure: vector width must be 0, 1 or 2 packs");
+      c->vec_packs = static_cast<int>(value);
+      return TBIK_OK;
+    case TBIK_AR_CFG_LOADS_IN_FLIGHT:
+      if (value < 0 || value > 32) return set_error(TBIK_ERR_ARG, "tbik_ar_configure: loads in flight must be 0..32");
+      c->loads_in_flight = static_cast<int>(value);
+      return TBIK_OK;
+    case TBIK_AR_CFG_TRACE:
+      if (value != 0 && c->trace_host == nullptr) {
+        cudaError_t e = cudaHostAlloc(reinterpret_cast<void**>(&c->trace_host), sizeof(uint64_t) * 8 * kMaxBlocks, cudaHostAllocMapped);
+        if (e != cudaSuccess) return set_cuda_error(e, "cudaHostAlloc(trace)");
+        memset(c->trace_host, 0, sizeof(uint64_t) * 8 * kMaxBlocks);
+        e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&c->trace_dev), c->trace_host, 0);
+        if (e != cudaSuccess) return set_cuda_error(e, "cudaHostGetDevicePointer(trace)");
+      } else if (value == 0 && c->trace_host != nullptr) {
+        cudaFreeHost(c->trace_host);
+        c->trace_host = c->trace_dev = nullptr;
+      }
       return TBIK_OK;
     case TBIK_AR_CFG_THREADS:
       if (value != 0 && (value < 32 || value > kThreads || value % 32 != 0))
@@ -575,6 +770,16 @@ int ar_register_graph_buffers(tbik_ar_t h, const void* const* handles, const int
   if (e != cudaSuccess) return set_cuda_error(e, "cudaMemcpy(graph rank data)");
   c->rd_next += n;
   c->graph_pending.clear();
+  return TBIK_OK;
+}
+
+int ar_trace(tbik_ar_t h, uint64_t* out, int max_blocks, int* blocks) {
+  Communicator* c = as_comm(h);
+  if (!c || !out || !blocks) return set_error(TBIK_ERR_ARG, "tbik_ar_trace: null pointer");
+  if (!c->trace_host) return set_error(TBIK_ERR_STATE, "tbik_ar_trace: tracing is off (TBIK_AR_CFG_TRACE)");
+  const int n = c->trace_blocks < max_blocks ? c->trace_blocks : max_blocks;
+  memcpy(out, c->trace_host, sizeof(uint64_t) * 8 * (n > 0 ? n : 0));
+  *blocks = n;
   return TBIK_OK;
 }
 

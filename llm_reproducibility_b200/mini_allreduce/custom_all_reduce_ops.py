@@ -61,9 +61,19 @@ def tree_matmul_allreduce(fa: int, A: torch.Tensor, B: torch.Tensor, reg_buffer:
     return _custom_ar.tree_matmul_allreduce(fa, A, B, reg_buffer, reg_buffer_sz_bytes, comm_ctas)
 
 
+def tree_all_reduce_within(fa: int, reg_base: int, byte_offset: int, out: torch.Tensor) -> None:
+    """Tree all-reduce of a message a producer wrote in place inside a registered buffer (addition)."""
+    _custom_ar.tree_all_reduce_within(fa, reg_base, byte_offset, out)
+
+
+def trace(fa: int) -> List[int]:
+    """Per-CTA phase time stamps of the last launch; needs configure(CFG_TRACE, 1) (addition)."""
+    return _custom_ar.trace(fa)
+
+
 # keys of `configure`
 CFG_SCRATCH_BYTES, CFG_ONESHOT_MAX_BYTES, CFG_MAX_BLOCKS, CFG_WAIT_LIMIT_NS, CFG_THREADS = 1, 2, 3, 4, 5
-CFG_PUSH_MIN_BYTES, CFG_PUSH_CHUNKS = 6, 7
+CFG_PUSH_MIN_BYTES, CFG_PUSH_CHUNKS, CFG_VEC_PACKS, CFG_LOADS_IN_FLIGHT, CFG_TRACE = 6, 7, 8, 9, 10
 
 
 def configure(fa: int, key: int, value: int) -> None:

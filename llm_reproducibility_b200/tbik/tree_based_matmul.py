@@ -56,7 +56,7 @@ def _workspace(device: torch.device, stream: int, nbytes: int) -> Optional[torch
 _WS_NEED = {}  # (device index, M, N, K, leaf) -> bytes of scratch the automatic schedule wants
 
 
-def _launch(A, W, C, M, N, K, leaf, dev) -> int:
+def _launch(A, W, C, M, N, K, leaf, dev, max_ctas=0) -> int:
     """Enqueue the GEMM on the current stream of `dev` (which must be the current device)."""
     L = _lib.lib()
     key = (dev.index, M, N, K, leaf)
@@ -65,6 +65,11 @@ def _launch(A, W, C, M, N, K, leaf, dev) -> int:
         need = _WS_NEED[key] = int(L.tbik_gemm_workspace_bytes(M, N, K, leaf))
     stream = torch.cuda.current_stream(dev).cuda_stream
     ws = _workspace(dev, stream, need)
+    if max_ctas > 0:
+        return L.tbik_gemm_ex(A.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K,
+                              max(A.stride(0), K), max(W.stride(0), K), max(C.stride(0), N),
+                              _DTYPE_CODE[A.dtype], leaf, _lib.NODE_INPUT, max_ctas, 0,
+                              ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, stream)
     return L.tbik_gemm_ws(A.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K,
                           max(A.stride(0), K), max(W.stride(0), K), max(C.stride(0), N),
                           _DTYPE_CODE[A.dtype], leaf, _lib.NODE_INPUT,
@@ -80,11 +85,13 @@ def prepare_operands(A: torch.Tensor, B: torch.Tensor):
 
 
 def matmul_tp_persistent(A: torch.Tensor, B: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                         *, leaf: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         *, leaf: Optional[int] = None, out: Optional[torch.Tensor] = None,
+                         max_ctas: int = 0) -> torch.Tensor:
     """C = A @ B with the K reduction in the fixed tree order; returns a new [M, N] tensor of A's dtype.
 
     A: [M, K]; B: [K, N] (any strides; a K-contiguous view such as `weight.t()` is used in place).
     `leaf` (keyword, extension) overrides the leaf width; the default is the reference's 256.
+    `max_ctas` (keyword, extension) bounds the CTAs of the launch (0 = one per SM); the bits do not depend on it.
     """
     assert A.shape[-1] == B.shape[-2], "Dim doesn't match"
     assert A.dim() == 2 and B.dim() == 2
@@ -104,10 +111,10 @@ def matmul_tp_persistent(A: torch.Tensor, B: torch.Tensor, bias: Optional[torch.
     assert C.shape == (M, N) and C.stride(1) == 1 and C.dtype == A.dtype
     dev = A.device
     if torch.cuda.current_device() == dev.index:
-        rc = _launch(A, W, C, M, N, K, leaf, dev)
+        rc = _launch(A, W, C, M, N, K, leaf, dev, max_ctas)
     else:
         with torch.cuda.device(dev):
-            rc = _launch(A, W, C, M, N, K, leaf, dev)
+            rc = _launch(A, W, C, M, N, K, leaf, dev, max_ctas)
     if rc != 0:
         _lib.check(rc, "tbik_gemm_ws")
     if bias is not None:

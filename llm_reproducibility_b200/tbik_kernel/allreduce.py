@@ -128,6 +128,29 @@ def _status(fa: int) -> List[int]:
     return list(out)
 
 
+def _tree_all_reduce_within(fa: int, reg_base: int, byte_offset: int, out: torch.Tensor) -> None:
+    """Tree all-reduce of `out.numel()` elements that lie `byte_offset` bytes into the registered buffer at
+    `reg_base` (written there in place by a producer kernel); the result goes to `out`."""
+    code = _DTYPE_CODE.get(out.dtype)
+    if code is None:
+        raise RuntimeError("custom allreduce only supports float32, float16 and bfloat16")
+    if not _is_weak_contiguous(out):
+        raise RuntimeError("out must be (weakly) contiguous")
+    with torch.cuda.device(out.device):
+        rc = _lib.lib().tbik_ar_tree_allreduce_within(fa, reg_base, byte_offset, out.data_ptr(), out.numel(), code,
+                                                      _stream_of(out))
+    _lib.check(rc, "tbik_ar_tree_allreduce_within")
+
+
+def _trace(fa: int) -> List[int]:
+    """Phase time stamps (ns) of the last launch, 8 per CTA, flattened (see tbik_ar_trace)."""
+    cap = 320
+    buf = (ctypes.c_uint64 * (8 * cap))()
+    n = ctypes.c_int()
+    _lib.check(_lib.lib().tbik_ar_trace(fa, buf, cap, ctypes.byref(n)), "tbik_ar_trace")
+    return [int(v) for v in buf[: 8 * n.value]]
+
+
 def _tree_matmul_allreduce(fa: int, A: torch.Tensor, B: torch.Tensor, reg_buffer: int, reg_buffer_sz_bytes: int,
                            comm_ctas: int = 0) -> torch.Tensor:
     """out = tree all-reduce over ranks of (A @ B), one kernel launch (tbik_ar_gemm_tree_allreduce)."""
@@ -189,6 +212,10 @@ def _register() -> None:
     lib.impl("configure", _configure, any_key)
     lib.define("status(int fa) -> int[]")
     lib.impl("status", _status, any_key)
+    lib.define("tree_all_reduce_within(int fa, int reg_base, int byte_offset, Tensor! out) -> ()")
+    lib.impl("tree_all_reduce_within", _tree_all_reduce_within, "CUDA")
+    lib.define("trace(int fa) -> int[]")
+    lib.impl("trace", _trace, any_key)
     lib.define("tree_matmul_allreduce(int fa, Tensor A, Tensor B, int reg_buffer, int reg_buffer_sz_bytes, "
                "int comm_ctas=0) -> Tensor")
     lib.impl("tree_matmul_allreduce", _tree_matmul_allreduce, "CUDA")
@@ -235,6 +262,14 @@ def meta_size(*args, **kwargs):
 
 def tree_matmul_allreduce(*args, **kwargs):
     return torch.ops.tbik_kernel.tree_matmul_allreduce.default(*args, **kwargs)
+
+
+def tree_all_reduce_within(*args, **kwargs):
+    return torch.ops.tbik_kernel.tree_all_reduce_within.default(*args, **kwargs)
+
+
+def trace(*args, **kwargs):
+    return torch.ops.tbik_kernel.trace.default(*args, **kwargs)
 
 
 def configure(*args, **kwargs):
