@@ -69,24 +69,27 @@ int tbik_gemm(const void* A, const void* W, void* C, int M, int N, int K, int64_
  * No counterpart in the reference (its kernel keeps the whole stack in registers). */
 size_t tbik_gemm_workspace_bytes(int M, int N, int64_t K, int leaf);
 
-/* As tbik_gemm, with a caller-owned scratch buffer (16-byte aligned device memory, contents
- * irrelevant before and after the call, not shared with a concurrently running call).  The
- * scratch serves the 256-column tilings (their accumulators fill tensor memory, so the upper
- * levels of the tree stack are kept in shared memory and, for levels touched at most once every
- * four leaves, in this buffer), trees deeper than the on-chip stack, and the K-slab roots of
- * decode-sized calls (below).  Same bits as tbik_gemm.
+/* As tbik_gemm, with a caller-owned scratch buffer (16-byte aligned device memory, not shared with a
+ * concurrently running call).  The buffer must be ZERO-FILLED ONCE before its first use (cudaMemset): its first
+ * 16 KiB hold arrival counters that every completed call leaves at zero again, so the same buffer serves call
+ * after call without further clearing; everything behind them may hold anything.  (If tbik_gemm_status ever
+ * reports a kernel that gave up, clear the buffer again.)  The scratch serves the 256-column tilings (their
+ * accumulators fill tensor memory, so the upper levels of the tree stack are kept in shared memory and, for
+ * levels touched at most once every four leaves, in this buffer), trees deeper than the on-chip stack, and the
+ * K-slab roots of decode-sized calls (below).  Same bits as tbik_gemm.
  * Replaces: the same reference functions as tbik_gemm. */
 int tbik_gemm_ws(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
                  int dtype, int leaf, int node_dtype, void* workspace, size_t workspace_bytes, tbik_stream_t stream);
 
 /* K-slabs.  When C has too few tiles to give every SM one (decode-sized M), tbik_gemm_ws cuts K into 2, 4, 8 or 16
- * slabs, each a whole subtree of the reduction tree, runs every (tile, slab) pair as its own work item, lets slab s
- * store its subtree root in the workspace and finishes the tree with a small second kernel that adds the roots
- * pairwise in the element type.  That is the arithmetic the reference applies across tensor-parallel ranks
+ * slabs, each a whole subtree of the reduction tree, and runs every (tile, slab) pair as its own work item of ONE
+ * launch.  Slab s stores its subtree root in the workspace and counts its arrival at the tile; the CTA that arrives
+ * last adds the roots pairwise in slab order in the element type and writes C (which CTA that is depends on timing,
+ * the sum it forms does not).  That is the arithmetic the reference applies across tensor-parallel ranks
  * (per-rank tree of K / tp, then the rank-pair tree: src/tbik/tree_based_matmul.py:240-249 with
  * mini_allreduce/tbik_kernel/csrc/allreduce/custom_all_reduce.cuh:203-234), applied inside one GPU, so the bits do
- * not change.  tbik_gemm_workspace_bytes includes the room for the roots.  tbik_gemm_slabs runs one explicit
- * (tiling 1..6, slabs = power of two <= min(16, T / F)) combination so that tests can prove the invariance;
+ * not change.  tbik_gemm_workspace_bytes includes the room for the roots and the counters.  tbik_gemm_slabs runs one
+ * explicit (tiling 1..6, slabs = power of two <= min(16, T / F)) combination so that tests can prove the invariance;
  * tbik_gemm_slabs_workspace_bytes gives its scratch need (0 for an invalid combination or when none is needed).
  * The functions themselves have no counterpart in the reference. */
 size_t tbik_gemm_slabs_workspace_bytes(int M, int N, int64_t K, int leaf, int tiling, int slabs);
@@ -108,13 +111,17 @@ int tbik_gemm_ex(const void* A, const void* W, void* C, int M, int N, int K, int
  * given all free HBM to its KV cache, where a cudaMalloc at this point would fail or stall.  The
  * scratch is a fixed array inside the library image (tbik_gemm_static_scratch_bytes() bytes, 32 MiB;
  * each GPU that loads the library keeps it until the process exits).  The call performs no
- * allocation of any kind.  Sizes whose scratch need (tbik_gemm_workspace_bytes) exceeds the array
- * are refused with TBIK_ERR_SHAPE and a message naming both numbers.  Same bits as tbik_gemm_ws.
+ * allocation of any kind.  It runs the schedule tbik_gemm_ws would pick if that one's scratch fits the
+ * array, else the best full-rate schedule that fits; sizes for which none fits (trees of more than about
+ * twelve levels at thousands of rows) are refused with TBIK_ERR_SHAPE and a message naming both numbers.
+ * Same bits as tbik_gemm_ws.
  * The first call on each device looks up the array's device address; make that first call outside
- * any stream capture.  All calls on a device share the one array, so two calls that can overlap on
- * the GPU (different streams) race on it -- serialise them.  The array keeps whatever the previous
- * call left behind; nothing in it needs clearing, because every word is written before it is read
- * within a call.
+ * any stream capture (two host threads may race on it harmlessly: both find the same address).  All
+ * calls on a device share the one array, so two calls that can overlap on the GPU (different streams)
+ * race on it -- serialise them.  The array keeps whatever the previous call left behind.  What must
+ * start at zero are the arrival counters at its head: they are zero when the library is loaded and
+ * every completed call puts them back to zero.  Everything else is written before it is read within a
+ * call (the rows of K-slab roots are padded to a multiple of 8 columns and the pad is written too).
  * This entry point has no counterpart in the reference. */
 int tbik_gemm_static(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
                      int dtype, int leaf, int node_dtype, tbik_stream_t stream);
@@ -122,6 +129,10 @@ int tbik_gemm_static(const void* A, const void* W, void* C, int M, int N, int K,
 /* Capacity in bytes of the scratch built into the library for tbik_gemm_static.
  * No counterpart in the reference. */
 size_t tbik_gemm_static_scratch_bytes(void);
+
+/* 1 if tbik_gemm_static would run these sizes on the current device, 0 if it would refuse them (a question
+ * about sizes only: nothing is launched, no pointer is needed).  No counterpart in the reference. */
+int tbik_gemm_static_accepts(int M, int N, int64_t K, int leaf);
 
 /* Reads (and clears) the device-side status of the GEMM kernels on the current device:
  * out[0] != 0 means a kernel gave up on a bounded wait (out[1] = block, out[2] = role).
@@ -211,25 +222,6 @@ int tbik_ar_status(tbik_ar_t comm, uint32_t out[8]);
  * has room for 8 * max_blocks values; *blocks receives the number of CTAs recorded.  This is how the phases of a
  * multi-rank kernel are timed without a profiler.  No counterpart in the reference. */
 int tbik_ar_trace(tbik_ar_t comm, uint64_t* out, int max_blocks, int* blocks);
-
-/* The whole row-split layer in ONE kernel launch: out = tree-all-reduce over ranks of (A * W^T), with the
- * K reduction of every rank in the fixed tree order and the cross-rank levels in the rank-pair order --
- * bitwise what tbik_gemm_ws followed by tbik_ar_tree_allreduce gives.  The last `comm_ctas` CTAs of the
- * grid (0 = built-in choice) do no multiplication: as soon as every rank has published an output tile they
- * pull the partial tiles over NVLink (plain peer loads), reduce the tiles this rank owns, and copy the
- * others from their owners, while the remaining CTAs keep computing later tiles.  `reg_buffer` is a
- * registered buffer of at least M*N*2 bytes that receives this rank's partial result (the GEMM writes it
- * directly; there is no staging copy); `workspace` as for tbik_gemm_ws
- * (tbik_ar_gemm_workspace_bytes).  N and ldo must be multiples of 8; 2, 4 or 8 ranks; not capturable.
- * Collective: every rank calls it in the same order with the same sizes.
- * Replaces: the sequence matmul_tp_persistent -> tree_all_reduce_sum in the patched forward,
- *           src/patch/patch_tp_invariant.py:31-34 (and the staging copy at custom_all_reduce.cu:112-114). */
-int tbik_ar_gemm_tree_allreduce(tbik_ar_t comm, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
-                                int64_t ldw, int64_t ldo, int dtype, int leaf, void* reg_buffer, size_t reg_buffer_bytes,
-                                void* workspace, size_t workspace_bytes, int comm_ctas, tbik_stream_t stream);
-
-/* Scratch bytes tbik_ar_gemm_tree_allreduce wants for these sizes (0 if none).  No counterpart in the reference. */
-size_t tbik_ar_gemm_workspace_bytes(int M, int N, int64_t K, int leaf);
 
 #ifdef __cplusplus
 }

@@ -32,6 +32,7 @@ _PROTOTYPES = {
     "tbik_gemm_slabs": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "tbik_gemm_static": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
     "tbik_gemm_static_scratch_bytes": (_sz, []),
+    "tbik_gemm_static_accepts": (_i32, [_i32, _i32, _i64, _i32]),
     "tbik_gemm_status": (_i32, [ctypes.POINTER(ctypes.c_uint32)]),
     "tbik_ar_meta_size": (_sz, []),
     "tbik_ar_create": (_i32, [ctypes.POINTER(_vp), _i32, _i32, _vp, _sz, _i32, ctypes.POINTER(_vp)]),
@@ -46,9 +47,6 @@ _PROTOTYPES = {
     "tbik_ar_graph_meta": (_i32, [_vp, _vp, ctypes.POINTER(_i64)]),
     "tbik_ar_register_graph_buffers": (_i32, [_vp, ctypes.POINTER(_vp), ctypes.POINTER(ctypes.POINTER(_i64))]),
     "tbik_ar_status": (_i32, [_vp, ctypes.POINTER(ctypes.c_uint32)]),
-    "tbik_ar_gemm_workspace_bytes": (_sz, [_i32, _i32, _i64, _i32]),
-    "tbik_ar_gemm_tree_allreduce": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _vp, _sz,
-                                            _vp, _sz, _i32, _vp]),
 }
 
 AR_CFG_SCRATCH_BYTES, AR_CFG_ONESHOT_MAX_BYTES, AR_CFG_MAX_BLOCKS, AR_CFG_WAIT_LIMIT_NS = 1, 2, 3, 4

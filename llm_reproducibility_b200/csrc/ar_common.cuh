@@ -1,5 +1,5 @@
-// Device-side pieces shared by the cross-GPU all-reduce kernels and by the GEMM kernel that reduces its
-// own output tiles over peer memory: the flag layout inside each rank's IPC-mapped meta buffer, the
+// Device-side pieces of the cross-GPU all-reduce kernels (the packed arithmetic is shared with the GEMM kernel,
+// which adds K-slab roots with it): the flag layout inside each rank's IPC-mapped meta buffer, the
 // peer-pointer record, bounded flag waits, the per-block epoch barrier and packed arithmetic.
 #pragma once
 
@@ -12,14 +12,9 @@ namespace tbik {
 constexpr int kMaxRanks = 8;
 constexpr int kMaxBlocks = 320;  // up to two CTAs per SM
 
-constexpr int kMaxTiles = 8192;  // output tiles per fused GEMM + all-reduce call
-
 struct alignas(128) Signal {
   uint32_t epoch[kMaxBlocks][kMaxRanks];  // private to the owning rank: last epoch used by (block, thread)
   uint32_t flag[kMaxBlocks][kMaxRanks];   // written by peers: flag[b][r] = last epoch announced by rank r, block b
-  // fused GEMM + all-reduce: written by the owning rank, read by its peers
-  uint32_t tile_ready[kMaxTiles];  // call number in which this rank's partial tile was last published
-  uint32_t tile_done[kMaxTiles];   // call number in which this rank last finished reducing the tile it owns
   // push schedule of the all-reduce: push_flag[b][r] is written by rank r's block b ("my reduced part of chunk c
   // of call k is in your scratch": (k << 12) + c + 1); push_calls[b] is private to the owning rank
   uint32_t push_flag[kMaxBlocks][kMaxRanks];

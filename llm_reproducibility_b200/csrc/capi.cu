@@ -69,6 +69,8 @@ int tbik_gemm_slabs(const void* A, const void* W, void* C, int M, int N, int K, 
 
 size_t tbik_gemm_static_scratch_bytes(void) { return tbik::gemm_static_scratch_bytes(); }
 
+int tbik_gemm_static_accepts(int M, int N, int64_t K, int leaf) { return tbik::gemm_static_accepts(M, N, K, leaf); }
+
 int tbik_gemm_static(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
                      int dtype, int leaf, int node_dtype, tbik_stream_t stream) {
   return tbik::gemm_launch_static(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype,
@@ -126,14 +128,5 @@ int tbik_ar_register_graph_buffers(tbik_ar_t comm, const void* const* handles, c
 }
 
 int tbik_ar_status(tbik_ar_t comm, uint32_t out[8]) { return tbik::ar_status(comm, out); }
-
-size_t tbik_ar_gemm_workspace_bytes(int M, int N, int64_t K, int leaf) { return tbik::gemm_fused_workspace_bytes(M, N, K, leaf); }
-
-int tbik_ar_gemm_tree_allreduce(tbik_ar_t comm, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
-                                int64_t ldw, int64_t ldo, int dtype, int leaf, void* reg_buffer, size_t reg_buffer_bytes,
-                                void* workspace, size_t workspace_bytes, int comm_ctas, tbik_stream_t stream) {
-  return tbik::ar_gemm_tree_allreduce(comm, A, W, out, M, N, K, lda, ldw, ldo, dtype, leaf, reg_buffer, reg_buffer_bytes,
-                                      workspace, workspace_bytes, comm_ctas, static_cast<cudaStream_t>(stream));
-}
 
 }  // extern "C"

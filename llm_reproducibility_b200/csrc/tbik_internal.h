@@ -19,25 +19,8 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
 size_t gemm_workspace_bytes(int M, int N, int64_t K, int leaf);
 size_t gemm_split_workspace_bytes(int M, int N, int64_t K, int leaf, int tiling, int splits);
 size_t gemm_static_scratch_bytes();
+int gemm_static_accepts(int M, int N, int64_t K, int leaf);
 
-// What the GEMM kernel needs from a communicator to reduce its own output tiles over peer memory.
-struct FusedArgs {
-  const void* rank_data_slot;  // device record with every rank's address of the registered partial buffer
-  const void* peer_parts[8];   // the same addresses on the host: rank k's partial buffer as mapped in this process
-  void* signals[8];            // every rank's meta buffer (flag area), as mapped in this process
-  void* status_dev;            // host-mapped status word (device address)
-  unsigned long long wait_limit_ns;
-  int world, rank, comm_ctas;
-  unsigned int epoch;          // number of this fused call: value the tile flags must reach
-  void* out;                   // final [M, N] result of this rank
-  long long ldo;
-};
-int gemm_launch_fused(const void* A, const void* W, void* part, int M, int N, int K, int64_t lda, int64_t ldw, int dtype,
-                      int leaf, void* workspace, size_t ws_bytes, const FusedArgs& fa, cudaStream_t stream);
-size_t gemm_fused_workspace_bytes(int M, int N, int64_t K, int leaf);
-int ar_gemm_tree_allreduce(tbik_ar_t h, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
-                           int64_t ldw, int64_t ldo, int dtype, int leaf, void* reg_buffer, size_t reg_bytes,
-                           void* workspace, size_t ws_bytes, int comm_ctas, cudaStream_t stream);
 int gemm_launch_static(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw,
                        int64_t ldc, int dtype, int leaf, int node_dtype, cudaStream_t stream);
 int gemm_status(uint32_t out[4]);

@@ -329,7 +329,6 @@ struct Communicator {
   RankData* rd_next = nullptr;  // next free slot of the caller-owned device table
   RankData* rd_end = nullptr;
   std::unordered_map<const void*, RankData*> registered;
-  std::unordered_map<const void*, RankData> registered_host;  // host copies of the records (for tensor maps)
   std::vector<void*> graph_pending;  // inputs seen during stream capture, slots reserved in order
   std::map<IpcKey, char*> opened;
   size_t scratch_bytes = 8u << 20;
@@ -348,7 +347,6 @@ struct Communicator {
   uint64_t* trace_host = nullptr;  // phase stamps of the last launch (host-mapped), when tracing is on
   uint64_t* trace_dev = nullptr;
   int trace_blocks = 0;
-  uint32_t tile_epoch = 0;  // fused GEMM + all-reduce calls made so far (same on every rank)
 };
 
 static Communicator* as_comm(tbik_ar_t h) { return reinterpret_cast<Communicator*>(h); }
@@ -562,42 +560,6 @@ int ar_run_within(tbik_ar_t h, const void* reg_base, size_t byte_offset, void* o
                      stream);
 }
 
-int ar_gemm_tree_allreduce(tbik_ar_t h, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
-                           int64_t ldw, int64_t ldo, int dtype, int leaf, void* reg_buffer, size_t reg_bytes,
-                           void* workspace, size_t ws_bytes, int comm_ctas, cudaStream_t stream) {
-  Communicator* c = as_comm(h);
-  if (!c) return set_error(TBIK_ERR_ARG, "fused GEMM + all-reduce: null communicator");
-  if (c->status_host && c->status_host->w[0] != 0) c->poisoned = true;
-  if (c->poisoned)
-    return set_error(TBIK_ERR_DEVICE, "all-reduce: an earlier call gave up waiting for a peer; the communicator must be rebuilt");
-  if (!reg_buffer) return set_error(TBIK_ERR_ARG, "fused GEMM + all-reduce needs a registered buffer for the partial results");
-  if (M > 0 && N > 0 && static_cast<size_t>(M) * N * 2 > reg_bytes)
-    return set_error(TBIK_ERR_SHAPE, "fused GEMM + all-reduce: partial result larger than the registered buffer");
-  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-  cudaError_t e = cudaStreamIsCapturing(stream, &cap);
-  if (e != cudaSuccess) return set_cuda_error(e, "cudaStreamIsCapturing");
-  if (cap == cudaStreamCaptureStatusActive)
-    return set_error(TBIK_ERR_STATE, "fused GEMM + all-reduce cannot be captured (its call number is a kernel argument)");
-  auto it = c->registered.find(reg_buffer);
-  if (it == c->registered.end()) return set_error(TBIK_ERR_STATE, "fused GEMM + all-reduce: buffer is not registered!");
-  FusedArgs fa{};
-  fa.rank_data_slot = it->second;
-  const RankData& host_rd = c->registered_host[reg_buffer];
-  for (int i = 0; i < c->world; ++i) fa.peer_parts[i] = host_rd.ptrs[i];
-  for (int i = 0; i < c->world; ++i) fa.signals[i] = c->sg.sig[i];
-  fa.status_dev = c->status_dev;
-  fa.wait_limit_ns = c->wait_limit_ns;
-  fa.world = c->world;
-  fa.rank = c->rank;
-  fa.comm_ctas = comm_ctas > 0 ? comm_ctas : (c->world <= 2 ? 16 : (c->world <= 4 ? 24 : 32));
-  fa.epoch = c->tile_epoch + 1;
-  fa.out = out;
-  fa.ldo = ldo;
-  int rc = gemm_launch_fused(A, W, reg_buffer, M, N, K, lda, ldw, dtype, leaf, workspace, ws_bytes, fa, stream);
-  if (rc == TBIK_OK) ++c->tile_epoch;  // validation is identical on every rank, so the counters stay in step
-  return rc;
-}
-
 size_t ar_meta_size() { return sizeof(Signal); }
 
 int ar_create(void* const* signals, int world, int rank, void* rank_data, size_t rank_data_bytes, int full_nvlink,
@@ -701,7 +663,6 @@ int ar_register_buffer(tbik_ar_t h, void* const* ptrs) {
   cudaError_t e = cudaMemcpy(c->rd_next, &d, sizeof(d), cudaMemcpyHostToDevice);
   if (e != cudaSuccess) return set_cuda_error(e, "cudaMemcpy(rank data)");
   c->registered[ptrs[c->rank]] = c->rd_next;
-  c->registered_host[ptrs[c->rank]] = d;
   ++c->rd_next;
   return TBIK_OK;
 }

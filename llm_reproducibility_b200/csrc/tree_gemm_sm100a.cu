@@ -36,6 +36,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <atomic>
+
 #include "ar_common.cuh"
 #include "ptx_sm100a.cuh"
 #include "tbik_internal.h"
@@ -53,19 +55,8 @@ constexpr int EPI_THREADS = NUM_EPI_WARPS * 32;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int CHUNK = 32;  // accumulator columns drained per tcgen05.ld
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
-
-// Fused GEMM + tree all-reduce: the last `comm_ctas` CTAs of the grid do not compute; they reduce and gather
-// finished output tiles over peer memory while the other CTAs keep multiplying.
-struct FusedDev {
-  const RankData* rd;   // every rank's partial-result buffer ([M, N] row-major, IPC registered)
-  RankSignals sg;       // every rank's flag area
-  ArStatus* status;
-  uint64_t limit_ns;
-  int world, rank, comm_ctas;
-  uint32_t epoch;
-  void* out;            // this rank's final [M, N]
-  int64_t ldo;
-};
+constexpr int kMaxSplits = 16;            // K-slabs per output tile
+constexpr size_t kCounterBytes = 16384;   // head of the workspace: one arrival counter per 128-row block of a tile
 
 struct GemmParams {
   void* C;
@@ -76,10 +67,14 @@ struct GemmParams {
   int tiles_m, tiles_n, group_m;  // tiles_m counts 128-row (single) or 256-row (pair) tiles
   uint32_t* scratch;     // global stack levels: [cta][level][chunk][word][epilogue thread]
   int scratch_levels;    // levels per CTA held in `scratch`
-  FusedDev f;            // used by the FUSED instantiation only
   int tma_store;         // 1: write C with TMA stores staged in the shared-memory stack slot (tmap_c valid)
   int splits;            // K-slabs per output tile (power of two); slab s covers leaves [s*T, (s+1)*T) and writes
   int64_t split_stride;  // its subtree root to C + s * split_stride elements (C = the partial buffer when > 1)
+  // K-slabs only: the CTA that stores the last of a tile's `splits` roots adds them and writes the result here
+  void* out;
+  int64_t ldo;
+  int n_out;             // true number of columns (N above is rounded up to 8 for the roots)
+  uint32_t* counters;    // arrivals per 128-row block of an output tile; zero before and after every launch
   uint32_t* status;      // [0] error code, [1] block, [2] role, [3] SM cycles of block 0 (last launch)
 };
 
@@ -105,7 +100,8 @@ struct Cfg {
   static constexpr uint32_t OFF_EPI_BAR = OFF_TEMPTY + 16;   // rendezvous of the 8 epilogue warps
   static constexpr uint32_t OFF_TMEM_PTR = OFF_EPI_BAR + 8;
   static constexpr uint32_t OFF_ABORT = OFF_TMEM_PTR + 4;
-  static constexpr uint32_t SMEM_BYTES = OFF_ABORT + 4 + 1024;   // + slack for the manual alignment
+  static constexpr uint32_t OFF_ARRIVE = OFF_ABORT + 4;          // K-slabs: this CTA's arrival number at its tile
+  static constexpr uint32_t SMEM_BYTES = OFF_ARRIVE + 4 + 1024;  // + slack for the manual alignment
   static_assert(BN == 32 || BN == 64 || BN == 128 || BN == 256, "BN");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
@@ -120,210 +116,50 @@ TBIK_DEVICE void tile_coords(const GemmParams& p, int tile, int& tm, int& tn) {
   tn = local / gsz;
 }
 
-// ------------------------------------------------------------------ communication CTAs of the fused kernel
-// Tile t is owned by rank t mod n.  The owner waits until every rank has published its partial tile,
-// adds them in the rank-pair tree order ((0+1)+(2+3))+((4+5)+(6+7)) in the element type (the upper
-// levels of the same reduction tree the GEMM started), writes the sum over its own partial tile and
-// into its result, and publishes "done"; every other rank then copies the owner's tile into its own
-// result.  Tiles are visited in the order the GEMM CTAs produce them, so the NVLink traffic of a tile
-// overlaps the UMMAs of later tiles.
-//
-// Peer data is pulled with tiled TMA loads (one destination CTA, peer memory as the source) into two
-// 64 KiB shared-memory buffers: the TMA unit keeps far more bytes in flight per SM than load
-// instructions can, which is what NVLink latency needs.  A job is one box column-block of an owned tile
-// (n loads, one per rank) or a whole tile to copy from its owner.  The next job is issued before the
-// current one is consumed only if its flags are already up, so a communication CTA never blocks on
-// another one while holding work that the other needs.  All waits are bounded; the final barrier keeps
-// every rank's buffers untouched until all ranks have finished reading.
-struct PeerMaps {
-  CUtensorMap m[8];  // rank k's partial-result buffer, box = 64 columns x (128 or 64) rows
-};
-
-constexpr uint32_t COMM_BUF_BYTES = 65536;
-constexpr int COMM_BUFS = 3;  // 192 KiB of loads in flight per communication CTA
-
-template <typename T, int NG, int BN>
-__device__ void comm_role_n(const GemmParams& p, const PeerMaps& maps, int cidx) {
-  static_assert(BN == 256, "communication role is written for 128x256 tiles");
-  constexpr int BOX_ROWS = NG == 8 ? 64 : 128;              // rows per 64-column box
-  constexpr uint32_t BOXB = BOX_ROWS * 128;                   // bytes of one box
-  constexpr int TILE_BOXES = (BM / BOX_ROWS) * (BN / 64);     // boxes of one tile (4 or 8), exactly one buffer
-  constexpr int OWN_BOXES = COMM_BUF_BYTES / (NG * BOXB);     // boxes (per rank) one "reduce" job covers
-  constexpr int OWN_JOBS = TILE_BOXES / OWN_BOXES;            // jobs per owned tile
-  static_assert(TILE_BOXES * BOXB == COMM_BUF_BYTES && OWN_BOXES >= 1 && OWN_JOBS * OWN_BOXES == TILE_BOXES, "buffer plan");
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ uint32_t fail;
-  __shared__ uint32_t inflight_s;
-  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* sgen = smem_raw + (sbase - smem_u32(smem_raw));
-  const uint32_t bar0 = sbase + COMM_BUFS * COMM_BUF_BYTES;
-  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(sgen + COMM_BUFS * COMM_BUF_BYTES + 64);
-  const FusedDev& f = p.f;
-  const int tid = threadIdx.x;
-  if (tid == 0) {
-    fail = 0u;
-    inflight_s = 0u;
-    *abort_flag = 0u;
-    for (int i = 0; i < COMM_BUFS; ++i) mbar_init(bar0 + 8u * i, 1);
-    fence_mbar_init();
-  }
-  __syncthreads();
-  const RankData rd = *f.rd;
-  Signal* self = f.sg.sig[f.rank];
-  const int num_tiles = p.tiles_m * p.tiles_n;
-  const int64_t row_packs = p.N / 8;  // 16-byte packs per row of the partial buffers
-  const int64_t out_row_packs = f.ldo / 8;
-  uint4* out = reinterpret_cast<uint4*>(f.out);
-  uint4* mine = reinterpret_cast<uint4*>(const_cast<void*>(rd.ptrs[f.rank]));
-
-  // job = (tile, sub): an owned tile is OWN_JOBS jobs, a tile to copy from its owner is one job
-  auto owned = [&](int t) { return t % NG == f.rank; };
-  auto advance = [&](int& t, int& sub) {
-    if (owned(t) && sub + 1 < OWN_JOBS) {
-      ++sub;
+// K-slabs: the upper levels of the tree.  `part` holds S subtree roots of one output element row by row
+// ([slab][row][column]); the result is their pairwise sum ((r0+r1)+(r2+r3))+..., every add rounded to the element
+// type -- the same nodes one CTA would have formed had it walked the whole of K, and the same arithmetic the
+// rank-pair tree all-reduce applies to tensor-parallel shards.  One thread handles `packs` consecutive 16-byte
+// packs of one row.  The roots were written by other CTAs of this launch: they are read past L1.
+template <typename T, int S>
+TBIK_DEVICE void combine_roots(const GemmParams& p, int row, int col0, int packs, bool vec_out) {
+  const uint4* part = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(p.C) + static_cast<int64_t>(row) * p.ldc);
+  const int64_t slab_packs = p.split_stride / 8;
+  T* orow = reinterpret_cast<T*>(p.out) + static_cast<int64_t>(row) * p.ldo;
+  constexpr int G = S < 8 ? S : 8;  // roots loaded at a time: a pairwise tree over 16 is the sum of two trees over 8
+  for (int k = 0; k < packs; ++k) {
+    const int c = col0 + 8 * k;
+    if (c >= p.N) break;  // p.N is a multiple of 8: a pack is inside the roots' row or outside as a whole
+    uint4 acc = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int g = 0; g < S / G; ++g) {
+      uint4 v[G];
+#pragma unroll
+      for (int sl = 0; sl < G; ++sl) v[sl] = __ldcg(part + (g * G + sl) * slab_packs + c / 8);
+#pragma unroll
+      for (int stride = 1; stride < G; stride *= 2) {
+#pragma unroll
+        for (int i = 0; i + stride < G; i += 2 * stride) v[i] = Elem<T>::add(v[i], v[i + stride]);
+      }
+      acc = g == 0 ? v[0] : Elem<T>::add(acc, v[0]);
+    }
+    if (vec_out && c + 8 <= p.n_out) {
+      *reinterpret_cast<uint4*>(orow + c) = acc;
     } else {
-      t += f.comm_ctas;
-      sub = 0;
-    }
-  };
-  auto box_xy = [&](int tm, int tn, int box, int& x, int& y) {
-    x = tn * BN + (box % (BN / 64)) * 64;
-    y = tm * BM + (box / (BN / 64)) * BOX_ROWS;
-  };
-  // thread 0: are the flags this job needs up?  block = wait for them (bounded)
-  auto flags_up = [&](int t, int sub, bool block) -> bool {
-    if (owned(t)) {
-      if (sub != 0) return true;  // checked with the tile's first job
-      for (int k = 0; k < NG; ++k) {
-        const uint32_t* fl = &f.sg.sig[k]->tile_ready[t];
-        if (block) {
-          if (!wait_flag_reached(fl, f.epoch, f.status, f.limit_ns, f.rank, k, 5)) return false;
-        } else if (static_cast<int32_t>(ld_flag_acquire(fl) - f.epoch) < 0) {
-          return false;
-        }
-      }
-      return true;
-    }
-    const int o = t % NG;
-    const uint32_t* fl = &f.sg.sig[o]->tile_done[t];
-    if (block) return wait_flag_reached(fl, f.epoch, f.status, f.limit_ns, f.rank, o, 6);
-    return static_cast<int32_t>(ld_flag_acquire(fl) - f.epoch) >= 0;
-  };
-  // thread 0: start the TMA loads of a job into buffer `slot`
-  auto issue = [&](int t, int sub, int slot) {
-    int tm, tn, x, y;
-    tile_coords(p, t, tm, tn);
-    const uint32_t dst = sbase + slot * COMM_BUF_BYTES;
-    const uint32_t bar = bar0 + 8u * slot;
-    asm volatile("fence.proxy.async;" ::: "memory");  // flags were read by loads; the data is read by the TMA unit
-    mbar_arrive_expect_tx(bar, COMM_BUF_BYTES);
-    if (owned(t)) {
+      const uint32_t w[4] = {acc.x, acc.y, acc.z, acc.w};
+      uint16_t* d16 = reinterpret_cast<uint16_t*>(orow + c);
 #pragma unroll
-      for (int ob = 0; ob < OWN_BOXES; ++ob) {
-        box_xy(tm, tn, sub * OWN_BOXES + ob, x, y);
-#pragma unroll
-        for (int k = 0; k < NG; ++k) tma_load_2d(dst + (ob * NG + k) * BOXB, &maps.m[k], x, y, bar);
-      }
-    } else {
-#pragma unroll
-      for (int bx = 0; bx < TILE_BOXES; ++bx) {
-        box_xy(tm, tn, bx, x, y);
-        tma_load_2d(dst + bx * BOXB, &maps.m[t % NG], x, y, bar);
-      }
-    }
-  };
-
-  int it = cidx, isub = 0, islot = 0;  // next job to issue (meaningful in thread 0)
-  int ct = cidx, csub = 0, cslot = 0;  // next job to consume (all threads)
-  uint32_t inflight = 0;               // thread 0's count of issued, not yet consumed jobs
-  uint32_t phases = 0;                 // bit s = parity to wait for on buffer s
-  while (true) {
-    if (tid == 0) {
-      // fill the ring; only block on flags when nothing is in flight, so that no communication CTA
-      // ever holds back work another one is waiting for
-      while (inflight < COMM_BUFS && it < num_tiles) {
-        const bool block = inflight == 0;
-        if (!flags_up(it, isub, block)) {
-          if (block) fail = 1u;
-          break;
-        }
-        issue(it, isub, islot);
-        advance(it, isub);
-        islot = islot + 1 == COMM_BUFS ? 0 : islot + 1;
-        ++inflight;
-      }
-      inflight_s = inflight;
-    }
-    __syncthreads();
-    if (fail != 0u || inflight_s == 0u) break;
-    if (!mbar_wait_bounded(bar0 + 8u * cslot, (phases >> cslot) & 1u, abort_flag, f.limit_ns)) fail = 1u;
-    phases ^= 1u << cslot;
-    __syncthreads();
-    if (fail != 0u) break;
-    // ---- consume the job in buffer cslot
-    int tm, tn;
-    tile_coords(p, ct, tm, tn);
-    const uint4* buf = reinterpret_cast<const uint4*>(sgen + cslot * COMM_BUF_BYTES);
-    if (owned(ct)) {
-      for (int i = tid; i < OWN_BOXES * BOX_ROWS * 8; i += blockDim.x) {
-        const int ob = i / (BOX_ROWS * 8), j = i - ob * (BOX_ROWS * 8);
-        uint4 v[NG];
-#pragma unroll
-        for (int k = 0; k < NG; ++k) v[k] = buf[(ob * NG + k) * (BOXB / 16) + j];
-#pragma unroll
-        for (int stride = 1; stride < NG; stride *= 2) {
-#pragma unroll
-          for (int k = 0; k + stride < NG; k += 2 * stride) v[k] = Elem<T>::add(v[k], v[k + stride]);
-        }
-        int x, y;
-        box_xy(tm, tn, csub * OWN_BOXES + ob, x, y);
-        const int r = y + (j >> 3);
-        const int64_t c = x / 8 + (j & 7);
-        if (r < p.M && c < row_packs) {
-          mine[static_cast<int64_t>(r) * row_packs + c] = v[0];
-          out[static_cast<int64_t>(r) * out_row_packs + c] = v[0];
-        }
-      }
-    } else {
-      for (int i = tid; i < TILE_BOXES * BOX_ROWS * 8; i += blockDim.x) {
-        const int bx = i / (BOX_ROWS * 8), j = i - bx * (BOX_ROWS * 8);
-        int x, y;
-        box_xy(tm, tn, bx, x, y);
-        const int r = y + (j >> 3);
-        const int64_t c = x / 8 + (j & 7);
-        if (r < p.M && c < row_packs) out[static_cast<int64_t>(r) * out_row_packs + c] = buf[i];
-      }
-    }
-    __syncthreads();  // the buffer is free again; this rank's stores of the job are issued
-    if (tid == 0) {
-      if (owned(ct) && csub == OWN_JOBS - 1) {
-        __threadfence_system();
-        st_flag_release(&self->tile_done[ct], f.epoch);
-      }
-      --inflight;
-    }
-    advance(ct, csub);
-    cslot = cslot + 1 == COMM_BUFS ? 0 : cslot + 1;
-  }
-  block_barrier<NG>(f.sg, self, f.rank, f.status, f.limit_ns, 7, &fail);
-}
-
-template <typename T, int BN>
-__device__ void comm_role(const GemmParams& p, const PeerMaps& maps, int cidx) {
-  if constexpr (BN == 256) {
-    switch (p.f.world) {
-      case 2: comm_role_n<T, 2, BN>(p, maps, cidx); break;
-      case 4: comm_role_n<T, 4, BN>(p, maps, cidx); break;
-      case 8: comm_role_n<T, 8, BN>(p, maps, cidx); break;
-      default: break;
+      for (int j = 0; j < 8; ++j)
+        if (c + j < p.n_out) d16[j] = static_cast<uint16_t>(j & 1 ? w[j >> 1] >> 16 : w[j >> 1] & 0xFFFFu);
     }
   }
 }
 
-template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR, bool FUSED = false>
+// SLABS: the instantiation that serves K-slab launches (p.splits > 1); the plain one carries none of that code.
+template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR, bool SLABS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_c, const GemmParams p, const __grid_constant__ PeerMaps peers) {
+                 const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
   using C_ = Cfg<BN, STAGES, SLEVELS, PAIR>;
   constexpr uint32_t STAGE_BYTES = C_::STAGE_BYTES;
   constexpr int TILE_M = C_::TILE_M;
@@ -336,14 +172,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n * p.splits;  // work items: (output tile, K-slab)
   // scheduling unit: a CTA, or a pair of CTAs (cluster of 2) working on one 256-row tile
-  static_assert(!(FUSED && PAIR), "the fused variant is single-CTA");
-  const int gemm_ctas = FUSED ? static_cast<int>(gridDim.x) - p.f.comm_ctas : static_cast<int>(gridDim.x);
-  if constexpr (FUSED) {
-    if (static_cast<int>(blockIdx.x) >= gemm_ctas) {
-      comm_role<T, BN>(p, peers, static_cast<int>(blockIdx.x) - gemm_ctas);
-      return;
-    }
-  }
+  const int gemm_ctas = static_cast<int>(gridDim.x);
   const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
   const int unit = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int num_units = PAIR ? gemm_ctas >> 1 : gemm_ctas;
@@ -620,22 +449,9 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       epi_phase ^= 1u;
     };
-    int pending_tile = -1;  // fused: tile whose stores are in flight and whose "ready" flag is still to be raised
-    auto publish_pending = [&]() {
-      if constexpr (FUSED) {
-        if (epi_tid == 0 && pending_tile >= 0) {
-          bulk_wait_all();  // the tile's global writes are performed
-          __threadfence_system();
-          st_flag_release(&p.f.sg.sig[p.f.rank]->tile_ready[pending_tile], p.f.epoch);
-          pending_tile = -1;
-        }
-      }
-    };
     auto staging_release = [&]() {
       if (staging_busy) {
-        if (epi_tid == 0) {
-          if constexpr (FUSED) publish_pending(); else bulk_wait_read_all();
-        }
+        if (epi_tid == 0) bulk_wait_read_all();
         epi_sync();
         staging_busy = false;
       }
@@ -654,6 +470,11 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * a);
+        }
+        if (SLABS && ok && p.splits > 1) {
+          // keep step with the two rendezvous of the draining warps' arrival protocol (below)
+          epi_sync();
+          if (ok) epi_sync();
         }
       }
     } else {
@@ -738,10 +559,10 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int b = 0; b < BN / 64; ++b) tma_store_2d(&tmap_c, sbase + b * (BM * 128), tn * BN + b * 64, row0);
             bulk_commit_group();
-            pending_tile = tile;
           }
           staging_busy = true;
-        } else if (row < p.M) {
+        } else {
+          if (row < p.M) {
           // root of the tile's tree: write this thread's BN/2 columns of C
 #pragma unroll
           for (int c = 0; c < NCH; ++c) {
@@ -761,10 +582,36 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               }
             }
           }
+          }
+          if (SLABS && p.splits > 1) {
+            // K-slabs: this was one of the tile's `splits` subtree roots.  Count the arrival; the CTA that brings
+            // the last root adds all of them in the fixed pairwise order and writes C.  Which CTA that is depends
+            // on timing, the sum does not: it is formed from all the roots, in slab order, by one thread per pack.
+            __threadfence();  // this thread's words of the root are visible device-wide before the arrival counts
+            epi_sync();
+            volatile uint32_t* arrive = reinterpret_cast<volatile uint32_t*>(smem_gen + C_::OFF_ARRIVE);
+            const uint32_t cidx = static_cast<uint32_t>(tile / p.splits) * (PAIR ? 2u : 1u) + cta_rank;
+            if (ok && epi_tid == 0) *arrive = atomicAdd(&p.counters[cidx], 1u);
+            if (ok) epi_sync();
+            if (ok && *arrive == static_cast<uint32_t>(p.splits) - 1u) {
+              __threadfence();  // the other CTAs' roots, published before their arrivals, are visible now
+              if (epi_tid == 0) p.counters[cidx] = 0u;  // nobody else counts on this tile in this launch any more
+              if (row < p.M) {
+                const bool vec_out = (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15u) == 0);
+                const int col0 = tn * BN + h * C_::COLS_PER_WARP;
+                constexpr int PACKS = C_::COLS_PER_WARP / 8;
+                switch (p.splits) {
+                  case 2: combine_roots<T, 2>(p, row, col0, PACKS, vec_out); break;
+                  case 4: combine_roots<T, 4>(p, row, col0, PACKS, vec_out); break;
+                  case 8: combine_roots<T, 8>(p, row, col0, PACKS, vec_out); break;
+                  default: combine_roots<T, 16>(p, row, col0, PACKS, vec_out); break;
+                }
+              }
+            }
+          }
         }
       }
     }
-    publish_pending();
     }  // draining warps
   }
 
@@ -787,44 +634,6 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 }
 
-// ------------------------------------------------------------------ K-slab combine
-// When a call has too few output tiles to give every SM one, K is cut into S slabs (S a power of two, each slab a
-// whole subtree of the reduction tree), every (tile, slab) pair becomes a work item of the GEMM kernel above, and
-// slab s writes its subtree root to part[s].  This kernel finishes the tree: out = the pairwise sum
-// ((p0+p1)+(p2+p3))+... of the roots, every add rounded to the element type -- the same upper tree levels one CTA
-// would have climbed, and the same arithmetic the rank-pair tree all-reduce applies to tensor-parallel shards.
-constexpr int kMaxSplits = 16;
-
-template <typename T, int S>
-__global__ void __launch_bounds__(256)
-slab_combine_kernel(const uint4* __restrict__ part, int64_t slab_packs, T* __restrict__ out, int M, int N, int64_t ldc,
-                    int ldp_packs, bool vec_ok) {
-  const int64_t total = static_cast<int64_t>(M) * ldp_packs;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    uint4 v[S];
-#pragma unroll
-    for (int k = 0; k < S; ++k) v[k] = part[k * slab_packs + i];
-#pragma unroll
-    for (int stride = 1; stride < S; stride *= 2) {
-#pragma unroll
-      for (int k = 0; k + stride < S; k += 2 * stride) v[k] = Elem<T>::add(v[k], v[k + stride]);
-    }
-    const int row = static_cast<int>(i / ldp_packs);
-    const int col0 = static_cast<int>(i % ldp_packs) * 8;
-    T* dst = out + static_cast<int64_t>(row) * ldc + col0;
-    if (vec_ok && col0 + 8 <= N) {
-      *reinterpret_cast<uint4*>(dst) = v[0];
-    } else {
-      const uint32_t w[4] = {v[0].x, v[0].y, v[0].z, v[0].w};
-      uint16_t* d16 = reinterpret_cast<uint16_t*>(dst);
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (col0 + j < N) d16[j] = static_cast<uint16_t>(j & 1 ? w[j >> 1] >> 16 : w[j >> 1] & 0xFFFFu);
-    }
-  }
-}
-
 // ==================================================================== host side
 namespace {
 
@@ -833,23 +642,51 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  // initialised once, by whichever thread comes first (C++11 guarantees the others wait)
+  static const EncodeTiledFn fn = [] {
     void* ptr = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess) {
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-  }
+        qres == cudaDriverEntryPointSuccess)
+      return reinterpret_cast<EncodeTiledFn>(ptr);
+    return static_cast<EncodeTiledFn>(nullptr);
+  }();
   return fn;
 }
+
+// Tensor maps are pure functions of (address, extents, stride, box, type): a layer that is called again with the
+// same weight and the same activation buffer (every decode step under a serving engine) finds its maps here
+// instead of paying three driver calls per launch.  One small direct-mapped table per host thread.
+struct TmapKey {
+  const void* base;
+  int64_t rows, K, ld;
+  int box_rows, dtype, swizzle;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && K == o.K && ld == o.ld && box_rows == o.box_rows && dtype == o.dtype &&
+           swizzle == o.swizzle;
+  }
+};
+struct TmapSlot {
+  TmapKey key{};
+  CUtensorMap map{};
+  bool valid = false;
+};
+constexpr int kTmapSlots = 256;
 
 // Row-major [rows, K] 16-bit matrix, row stride `ld` elements, box = 64 (K) x `box_rows` rows.
 int make_tmap(CUtensorMap* tm, int dtype, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows,
               bool quiet = false, bool swizzle = true) {
+  static thread_local TmapSlot cache[kTmapSlots];
+  const TmapKey key{base, rows, K, ld, box_rows, dtype, swizzle ? 1 : 0};
+  uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
+  h ^= static_cast<uint64_t>(rows) * 0x9E3779B97F4A7C15ull;
+  h ^= static_cast<uint64_t>(K) * 0xC2B2AE3D27D4EB4Full + static_cast<uint64_t>(box_rows);
+  h ^= h >> 29;
+  TmapSlot& slot = cache[h % kTmapSlots];
+  if (slot.valid && slot.key == key) {
+    *tm = slot.map;
+    return TBIK_OK;
+  }
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return set_error(TBIK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
@@ -867,26 +704,42 @@ int make_tmap(CUtensorMap* tm, int dtype, const void* base, int64_t rows, int64_
              (long long)rows, (long long)K, (long long)ld);
     return set_error(TBIK_ERR_CUDA, msg);
   }
+  slot.key = key;
+  slot.map = *tm;
+  slot.valid = true;
   return TBIK_OK;
 }
 
 __device__ uint32_t g_gemm_status[4];
 
-template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR, bool FUSED = false>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
-           cudaStream_t stream, const PeerMaps* peers = nullptr) {
-  static const PeerMaps no_peers{};
-  const PeerMaps& pm = peers ? *peers : no_peers;
+constexpr int kMaxDevices = 64;
+
+// Device address of the status word, looked up once per device.
+uint32_t* status_address(int dev) {
+  static std::atomic<uint32_t*> addr[kMaxDevices];
+  if (dev < 0 || dev >= kMaxDevices) return nullptr;
+  uint32_t* p = addr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    void* q = nullptr;
+    if (cudaGetSymbolAddress(&q, g_gemm_status) != cudaSuccess) return nullptr;
+    p = static_cast<uint32_t*>(q);
+    addr[dev].store(p, std::memory_order_release);
+  }
+  return p;
+}
+
+template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR, bool SLABS>
+int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
+           cudaStream_t stream, int dev) {
   using C_ = Cfg<BN, STAGES, SLEVELS, PAIR>;
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  auto kernel = tree_gemm_kernel<T, BN, STAGES, SLEVELS, PAIR, FUSED>;
-  if (dev < 64 && !configured[dev]) {
+  // set twice at worst when two threads race on a device's first launch: the call is idempotent
+  static std::atomic<bool> configured[kMaxDevices];
+  auto kernel = tree_gemm_kernel<T, BN, STAGES, SLEVELS, PAIR, SLABS>;
+  if (dev >= 0 && dev < kMaxDevices && !configured[dev].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(C_::SMEM_BYTES));
     if (e != cudaSuccess) return set_cuda_error(e, "cudaFuncSetAttribute(tree_gemm_kernel)");
-    configured[dev] = true;
+    configured[dev].store(true, std::memory_order_release);
   }
   if constexpr (PAIR) {
     cudaLaunchConfig_t cfg{};
@@ -901,14 +754,21 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, p, pm);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, ta, tb, tc, p);
     if (e != cudaSuccess) return set_cuda_error(e, "tree_gemm_kernel launch");
   } else {
-    kernel<<<grid, NUM_THREADS, C_::SMEM_BYTES, stream>>>(ta, tb, tc, p, pm);
+    kernel<<<grid, NUM_THREADS, C_::SMEM_BYTES, stream>>>(ta, tb, tc, p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return set_cuda_error(e, "tree_gemm_kernel launch");
   }
   return TBIK_OK;
+}
+
+template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
+           cudaStream_t stream, int dev) {
+  return p.splits > 1 ? launch_one<T, BN, STAGES, SLEVELS, PAIR, true>(ta, tb, tc, p, grid, stream, dev)
+                      : launch_one<T, BN, STAGES, SLEVELS, PAIR, false>(ta, tb, tc, p, grid, stream, dev);
 }
 
 // The compiled variants.  `levels_on_chip` = stack levels above level 0 that fit TMEM + shared memory.
@@ -937,29 +797,34 @@ constexpr Variant kVariants[6][2] = {
 
 template <typename T>
 int launch_variant(int tiling, bool deep, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                   const GemmParams& p, int grid, cudaStream_t stream) {
+                   const GemmParams& p, int grid, cudaStream_t stream, int dev) {
   switch (tiling) {
-    case 1: return deep ? launch<T, 128, 4, 2, false>(ta, tb, tc, p, grid, stream) : launch<T, 128, 6, 0, false>(ta, tb, tc, p, grid, stream);
-    case 2: return deep ? launch<T, 128, 5, 2, true>(ta, tb, tc, p, grid, stream) : launch<T, 128, 8, 0, true>(ta, tb, tc, p, grid, stream);
-    case 3: return launch<T, 256, 3, 1, false>(ta, tb, tc, p, grid, stream);
-    case 4: return launch<T, 256, 5, 1, true>(ta, tb, tc, p, grid, stream);
-    case 5: return launch<T, 64, 8, 0, false>(ta, tb, tc, p, grid, stream);
-    case 6: return launch<T, 32, 8, 0, false>(ta, tb, tc, p, grid, stream);
+    case 1: return deep ? launch<T, 128, 4, 2, false>(ta, tb, tc, p, grid, stream, dev) : launch<T, 128, 6, 0, false>(ta, tb, tc, p, grid, stream, dev);
+    case 2: return deep ? launch<T, 128, 5, 2, true>(ta, tb, tc, p, grid, stream, dev) : launch<T, 128, 8, 0, true>(ta, tb, tc, p, grid, stream, dev);
+    case 3: return launch<T, 256, 3, 1, false>(ta, tb, tc, p, grid, stream, dev);
+    case 4: return launch<T, 256, 5, 1, true>(ta, tb, tc, p, grid, stream, dev);
+    case 5: return launch<T, 64, 8, 0, false>(ta, tb, tc, p, grid, stream, dev);
+    case 6: return launch<T, 32, 8, 0, false>(ta, tb, tc, p, grid, stream, dev);
     default: return set_error(TBIK_ERR_ARG, "unknown tiling");
   }
 }
 
-int sm_count() {
-  static int cached[64] = {};
+int sm_count(int dev) {
+  static std::atomic<int> cached[kMaxDevices];
+  if (dev < 0 || dev >= kMaxDevices) dev = 0;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 1;
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
+int current_device() {
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 64) dev = 0;
-  if (cached[dev] == 0) {
-    int n = 0;
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    cached[dev] = n > 0 ? n : 1;
-  }
-  return cached[dev];
+  return dev;
 }
 
 }  // namespace
@@ -980,6 +845,7 @@ int tree_shape(int64_t K, int leaf, int* T, int* F, int* L) {
 }
 
 // Schedule for one call: which variant, how many CTAs, how much scratch.
+// Workspace layout: [arrival counters, kCounterBytes, only with K-slabs][global stack levels][slab roots].
 struct Plan {
   int tiling;  // 1..6
   bool deep;
@@ -988,9 +854,11 @@ struct Plan {
   int splits;             // K-slabs per output tile (1 = the whole tree in one CTA)
   int slab_levels;        // tree levels one work item climbs: L - log2(splits)
   int scratch_levels;
+  size_t scratch_off;     // offset of the global stack levels in the workspace
   size_t scratch_bytes;   // global stack levels
   size_t partial_off;     // offset of the slab roots in the workspace (0 when splits == 1)
   size_t partial_bytes;   // [splits][M][N rounded up to 8] elements
+  bool valid;
   size_t total_bytes() const { return splits > 1 ? partial_off + partial_bytes : scratch_bytes; }
 };
 
@@ -1005,6 +873,7 @@ static Plan make_plan(int tiling, int M, int N, int L, int max_ctas, int splits 
   Plan pl{};
   pl.tiling = tiling;
   pl.splits = splits;
+  pl.valid = true;
   L -= log2_int(splits);
   pl.slab_levels = L;
   const Variant& shallow = kVariants[tiling - 1][0];
@@ -1014,7 +883,7 @@ static Plan make_plan(int tiling, int M, int N, int L, int max_ctas, int splits 
   pl.tiles_m = (M + tile_m - 1) / tile_m;
   pl.tiles_n = (N + v.bn - 1) / v.bn;
   const int num_tiles = pl.tiles_m * pl.tiles_n * splits;
-  int ctas = sm_count();
+  int ctas = sm_count(current_device());
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   int units = v.pair ? ctas / 2 : ctas;
   if (units < 1) units = 1;
@@ -1023,7 +892,10 @@ static Plan make_plan(int tiling, int M, int N, int L, int max_ctas, int splits 
   pl.scratch_levels = (L - 1) > v.levels_on_chip ? (L - 1) - v.levels_on_chip : 0;
   pl.scratch_bytes = static_cast<size_t>(pl.grid) * pl.scratch_levels * v.level_bytes;
   if (splits > 1) {
-    pl.partial_off = (pl.scratch_bytes + 255) & ~size_t(255);
+    // one arrival counter per 128-row block of an output tile
+    if (static_cast<size_t>(pl.tiles_m) * pl.tiles_n * (v.pair ? 2 : 1) * sizeof(uint32_t) > kCounterBytes) pl.valid = false;
+    pl.scratch_off = kCounterBytes;
+    pl.partial_off = (pl.scratch_off + pl.scratch_bytes + 255) & ~size_t(255);
     pl.partial_bytes = static_cast<size_t>(splits) * M * ((N + 7) / 8 * 8) * 2;
   }
   return pl;
@@ -1031,7 +903,7 @@ static Plan make_plan(int tiling, int M, int N, int L, int max_ctas, int splits 
 
 // Rough time of a plan in microseconds, fitted to measurements at 16..512 rows of C (N = 4096, K = 1536..12288):
 // a CTA advances one 64-wide k-block every 0.155 us (32-column tile) .. 0.53 us (256 columns), launch and
-// prologue cost 3.5 us, the combine kernel 2.5 us plus its bytes.  What counts is the k-blocks per CTA.
+// prologue cost 3.5 us; with K-slabs the last CTA of every tile re-reads the slab roots (from L2) and adds them.
 static double plan_cost_us(const Plan& pl, int M, int N, int kblocks_total, int ctas) {
   const Variant& v = kVariants[pl.tiling - 1][pl.deep ? 1 : 0];
   const int items = pl.tiles_m * pl.tiles_n * pl.splits;
@@ -1039,7 +911,7 @@ static double plan_cost_us(const Plan& pl, int M, int N, int kblocks_total, int 
   const int waves = (items + units - 1) / (units > 0 ? units : 1);
   const double per_kblock = v.bn >= 256 ? 0.53 : v.bn == 128 ? (v.pair ? 0.18 : 0.23) : v.bn == 64 ? 0.17 : 0.155;
   double t = 3.5 + waves * (kblocks_total / pl.splits) * per_kblock;
-  if (pl.splits > 1) t += 2.5 + static_cast<double>(pl.splits + 1) * M * N * 2 / 3.0e6;  // combine launch + its bytes at 3 TB/s
+  if (pl.splits > 1) t += 0.8 + 0.12 * pl.splits + static_cast<double>(pl.splits + 1) * M * N * 2 / 3.0e6;
   return t;
 }
 
@@ -1052,7 +924,7 @@ static double plan_cost_us(const Plan& pl, int M, int N, int kblocks_total, int 
 // (tiling, slabs) that fits one wave and the caller's workspace is costed and the cheapest wins.  `groups` is the
 // number of level-0 groups of the tree (T / F), the finest cut that keeps every slab a whole subtree.
 static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int max_ctas, size_t ws_bytes, bool have_ws) {
-  int ctas = sm_count();
+  int ctas = sm_count(current_device());
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   const int enough = ctas - ctas / 5;
   // short K (at most 6 leaves of 256): the per-tile costs (pipeline refill, storing C) weigh more than the
@@ -1087,7 +959,7 @@ static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int ma
     for (int s = 2; s <= kMaxSplits && s <= groups; s *= 2) {
       Plan pl = make_plan(order[i], M, N, L, max_ctas, s);
       if (pl.tiles_m * pl.tiles_n * s * (kVariants[order[i] - 1][0].pair ? 2 : 1) > ctas) break;  // one wave only
-      if (pl.total_bytes() > ws_bytes) continue;
+      if (!pl.valid || pl.total_bytes() > ws_bytes) continue;
       const double c = plan_cost_us(pl, M, N, kblocks_total, ctas);
       if (c < best_cost) {
         best = pl;
@@ -1109,70 +981,16 @@ size_t gemm_split_workspace_bytes(int M, int N, int64_t K, int leaf, int tiling,
   int T, F, L;
   if (M <= 0 || N <= 0 || tree_shape(K, leaf, &T, &F, &L) != TBIK_OK) return 0;
   if (tiling < 1 || tiling > 6 || splits < 1 || splits > kMaxSplits || (splits & (splits - 1)) || splits > T / F) return 0;
-  return make_plan(tiling, M, N, L, 0, splits).total_bytes();
+  const Plan pl = make_plan(tiling, M, N, L, 0, splits);
+  return pl.valid ? pl.total_bytes() : 0;
 }
 
-template <typename T>
-static int launch_combine(int splits, const void* part, T* out, int M, int N, int64_t ldc, cudaStream_t stream) {
-  const int ldp_packs = (N + 7) / 8;
-  const int64_t slab_packs = static_cast<int64_t>(M) * ldp_packs;
-  const bool vec_ok = (reinterpret_cast<uintptr_t>(out) & 15u) == 0 && ldc % 8 == 0;
-  int64_t blocks = (slab_packs + 255) / 256;
-  const int cap = sm_count() * 8;
-  if (blocks > cap) blocks = cap;
-  const uint4* p4 = static_cast<const uint4*>(part);
-  const int g = static_cast<int>(blocks);
-  switch (splits) {
-    case 2: slab_combine_kernel<T, 2><<<g, 256, 0, stream>>>(p4, slab_packs, out, M, N, ldc, ldp_packs, vec_ok); break;
-    case 4: slab_combine_kernel<T, 4><<<g, 256, 0, stream>>>(p4, slab_packs, out, M, N, ldc, ldp_packs, vec_ok); break;
-    case 8: slab_combine_kernel<T, 8><<<g, 256, 0, stream>>>(p4, slab_packs, out, M, N, ldc, ldp_packs, vec_ok); break;
-    case 16: slab_combine_kernel<T, 16><<<g, 256, 0, stream>>>(p4, slab_packs, out, M, N, ldc, ldp_packs, vec_ok); break;
-    default: return set_error(TBIK_ERR_ARG, "slab combine: unsupported slab count");
-  }
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return set_cuda_error(e, "slab combine kernel launch");
-  return TBIK_OK;
-}
-
-int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
-                int dtype, int leaf, int node_dtype, int max_ctas, int tiling, void* workspace, size_t ws_bytes,
-                cudaStream_t stream, int splits) {
-  if (dtype != TBIK_DTYPE_BF16 && dtype != TBIK_DTYPE_FP16)
-    return set_error(TBIK_ERR_DTYPE, "tbik_gemm supports bf16 and fp16 operands");
-  if (node_dtype != TBIK_NODE_INPUT)
-    return set_error(TBIK_ERR_DTYPE, "tbik_gemm: only node_dtype = TBIK_NODE_INPUT is implemented");
-  if (M < 0 || N < 0 || K <= 0) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: M, N must be >= 0 and K > 0");
-  if (leaf <= 0 || leaf % BK != 0) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: leaf must be a positive multiple of 64");
-  if (tiling < 0 || tiling > 6) return set_error(TBIK_ERR_ARG, "tbik_gemm: tiling must be 0..6");
-  int T, F, L;
-  if (tree_shape(K, leaf, &T, &F, &L) != TBIK_OK)
-    return set_error(TBIK_ERR_SHAPE, "tbik_gemm: K must be a multiple of the leaf width");
-  if (L > 16) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: reduction tree deeper than 16 levels is not supported");
-  if (M == 0 || N == 0) return TBIK_OK;
-  if (!A || !W || !C) return set_error(TBIK_ERR_ARG, "tbik_gemm: null pointer");
-  if (lda < K || ldw < K || ldc < N) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: leading dimension smaller than the row");
-  if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(W) & 15u) || (lda % 8) || (ldw % 8))
-    return set_error(TBIK_ERR_ALIGN, "tbik_gemm: A and W must be 16-byte aligned with row strides that are multiples of 8 elements");
-  if (reinterpret_cast<uintptr_t>(C) & 1u) return set_error(TBIK_ERR_ALIGN, "tbik_gemm: C must be 2-byte aligned");
-  if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 15u))
-    return set_error(TBIK_ERR_ALIGN, "tbik_gemm: workspace must be 16-byte aligned");
-  const bool have_ws = workspace != nullptr && ws_bytes > 0;
-
-  // splits: 0 = automatic (only together with tiling 0), 1 = none, else a power of two of whole subtrees
-  if (splits < 0 || splits > kMaxSplits || (splits & (splits - 1)) != 0)
-    return set_error(TBIK_ERR_ARG, "tbik_gemm: the number of K-slabs must be a power of two up to 16");
-  if (splits > 1 && (tiling == 0 || splits > T / F))
-    return set_error(TBIK_ERR_SHAPE, "tbik_gemm: K-slabs need an explicit tiling and at most T / F slabs (whole subtrees)");
-  const Plan pl = tiling == 0 ? auto_plan(M, N, L, splits == 1 ? 1 : T / F, T * (leaf / BK), max_ctas, ws_bytes, have_ws)
-                              : make_plan(tiling, M, N, L, max_ctas, splits > 1 ? splits : 1);
-  if (pl.total_bytes() > 0 && (!have_ws || pl.total_bytes() > ws_bytes)) {
-    char msg[200];
-    snprintf(msg, sizeof(msg),
-             "tbik_gemm: a reduction tree of %d levels needs %zu bytes of scratch for this tiling (got %zu); "
-             "see tbik_gemm_workspace_bytes", L, pl.total_bytes(), have_ws ? ws_bytes : size_t(0));
-    return set_error(TBIK_ERR_SHAPE, msg);
-  }
+// `forced` (optional): a plan chosen by the caller (the entry point with built-in scratch picks one that fits it).
+static int gemm_launch_plan(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw,
+                            int64_t ldc, int dtype, int leaf, int T, int F, const Plan& pl, void* workspace,
+                            cudaStream_t stream) {
   const Variant& v = kVariants[pl.tiling - 1][pl.deep ? 1 : 0];
+  const int dev = current_device();
 
   CUtensorMap ta, tb;
   int rc = make_tmap(&ta, dtype, A, M, K, lda, BM);
@@ -1194,149 +1012,148 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
   p.tiles_m = pl.tiles_m;
   p.tiles_n = pl.tiles_n;
   p.group_m = v.pair ? 8 : 16;  // 2048 rows of A per group: a wave of CTAs covers a near-square block of C
-  p.scratch = static_cast<uint32_t*>(workspace);
+  p.scratch = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) + pl.scratch_off);
   p.scratch_levels = pl.scratch_levels;
-  void* status_ptr = nullptr;
-  cudaGetSymbolAddress(&status_ptr, g_gemm_status);
-  p.status = static_cast<uint32_t*>(status_ptr);
+  p.status = status_address(dev);
 
   // C through TMA stores when its layout allows a tensor map (64-column boxes of 128 rows); otherwise the
   // epilogue threads store their rows directly.
   CUtensorMap tc{};
   p.tma_store = 0;
   if (pl.splits > 1) {
-    // slab roots go to the workspace with direct stores; the combine kernel writes C
+    // slab roots go to the workspace with direct stores (pad columns up to a multiple of 8 included: they are
+    // zeros, W has no such rows); the CTA that stores the last root of a tile adds the roots and writes C
     const int64_t ldp = (N + 7) / 8 * 8;
+    p.out = C;
+    p.ldo = ldc;
+    p.n_out = N;
     p.C = static_cast<unsigned char*>(workspace) + pl.partial_off;
     p.ldc = ldp;
+    p.N = static_cast<int>(ldp);
     p.split_stride = static_cast<int64_t>(M) * ldp;
+    p.counters = static_cast<uint32_t*>(workspace);
   } else if ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && ldc % 8 == 0 &&
              make_tmap(&tc, dtype, C, M, N, ldc, BM, true) == TBIK_OK) {
     p.tma_store = 1;
   }
 
-  rc = dtype == TBIK_DTYPE_BF16 ? launch_variant<__nv_bfloat16>(pl.tiling, pl.deep, ta, tb, tc, p, pl.grid, stream)
-                                : launch_variant<__half>(pl.tiling, pl.deep, ta, tb, tc, p, pl.grid, stream);
-  if (rc != TBIK_OK || pl.splits == 1) return rc;
-  if (dtype == TBIK_DTYPE_BF16)
-    return launch_combine<__nv_bfloat16>(pl.splits, p.C, static_cast<__nv_bfloat16*>(C), M, N, ldc, stream);
-  return launch_combine<__half>(pl.splits, p.C, static_cast<__half*>(C), M, N, ldc, stream);
+  return dtype == TBIK_DTYPE_BF16 ? launch_variant<__nv_bfloat16>(pl.tiling, pl.deep, ta, tb, tc, p, pl.grid, stream, dev)
+                                  : launch_variant<__half>(pl.tiling, pl.deep, ta, tb, tc, p, pl.grid, stream, dev);
 }
 
-// ---------------------------------------------------------------- GEMM + tree all-reduce in one launch
-int gemm_launch_fused(const void* A, const void* W, void* part, int M, int N, int K, int64_t lda, int64_t ldw, int dtype,
-                      int leaf, void* workspace, size_t ws_bytes, const FusedArgs& fa, cudaStream_t stream) {
+static int gemm_check_args(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw,
+                           int64_t ldc, int dtype, int leaf, int node_dtype, int tiling, const void* workspace, int* T,
+                           int* F, int* L) {
   if (dtype != TBIK_DTYPE_BF16 && dtype != TBIK_DTYPE_FP16)
-    return set_error(TBIK_ERR_DTYPE, "fused GEMM + all-reduce supports bf16 and fp16");
-  if (fa.world != 2 && fa.world != 4 && fa.world != 8)
-    return set_error(TBIK_ERR_SHAPE, "fused GEMM + all-reduce supports 2, 4 or 8 ranks");
-  if (M <= 0 || N <= 0 || K <= 0 || N % 8 != 0 || fa.ldo % 8 != 0 || fa.ldo < N)
-    return set_error(TBIK_ERR_SHAPE, "fused GEMM + all-reduce: M, N, K > 0 and N, ldo multiples of 8");
-  if (leaf <= 0 || leaf % BK != 0) return set_error(TBIK_ERR_SHAPE, "leaf must be a positive multiple of 64");
-  int T, F, L;
-  if (tree_shape(K, leaf, &T, &F, &L) != TBIK_OK || L > 16)
-    return set_error(TBIK_ERR_SHAPE, "K must be a multiple of the leaf width (tree of at most 16 levels)");
-  if (!A || !W || !part || !fa.out) return set_error(TBIK_ERR_ARG, "fused GEMM + all-reduce: null pointer");
-  if (lda < K || ldw < K) return set_error(TBIK_ERR_SHAPE, "leading dimension smaller than the row");
-  if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(W) & 15u) || (lda % 8) || (ldw % 8) ||
-      (reinterpret_cast<uintptr_t>(part) & 15u) || (reinterpret_cast<uintptr_t>(fa.out) & 15u) ||
-      (workspace && (reinterpret_cast<uintptr_t>(workspace) & 15u)))
-    return set_error(TBIK_ERR_ALIGN, "fused GEMM + all-reduce: operands must be 16-byte aligned, strides multiples of 8");
-  const int sms = sm_count();
-  int comm = fa.comm_ctas;
-  if (comm < 2 || comm > sms / 2) return set_error(TBIK_ERR_ARG, "fused GEMM + all-reduce: comm_ctas out of range");
-  const Plan pl = make_plan(3, M, N, L, sms - comm);
-  if (pl.tiles_m * pl.tiles_n > kMaxTiles) return set_error(TBIK_ERR_SHAPE, "fused GEMM + all-reduce: too many output tiles");
-  if (pl.scratch_bytes > 0 && (workspace == nullptr || pl.scratch_bytes > ws_bytes))
-    return set_error(TBIK_ERR_SHAPE, "fused GEMM + all-reduce: scratch buffer too small for this tree");
-  const Variant& v = kVariants[2][0];
-  CUtensorMap ta, tb, tc;
-  int rc = make_tmap(&ta, dtype, A, M, K, lda, BM);
-  if (rc != TBIK_OK) return rc;
-  rc = make_tmap(&tb, dtype, W, N, K, ldw, v.bn);
-  if (rc != TBIK_OK) return rc;
-  rc = make_tmap(&tc, dtype, part, M, N, N, BM);
-  if (rc != TBIK_OK) return rc;
-  GemmParams p{};
-  p.C = part;
-  p.ldc = N;
-  p.M = M;
-  p.N = N;
-  p.kblocks_per_leaf = leaf / BK;
-  p.T = T;
-  p.F = F;
-  p.L = L;
-  p.tiles_m = pl.tiles_m;
-  p.tiles_n = pl.tiles_n;
-  p.group_m = 16;
-  p.splits = 1;
-  p.scratch = static_cast<uint32_t*>(workspace);
-  p.scratch_levels = pl.scratch_levels;
-  p.tma_store = 1;
-  void* status_ptr = nullptr;
-  cudaGetSymbolAddress(&status_ptr, g_gemm_status);
-  p.status = static_cast<uint32_t*>(status_ptr);
-  p.f.rd = static_cast<const RankData*>(fa.rank_data_slot);
-  for (int i = 0; i < fa.world; ++i) p.f.sg.sig[i] = static_cast<Signal*>(fa.signals[i]);
-  p.f.status = static_cast<ArStatus*>(fa.status_dev);
-  p.f.limit_ns = fa.wait_limit_ns;
-  p.f.world = fa.world;
-  p.f.rank = fa.rank;
-  p.f.comm_ctas = comm;
-  p.f.epoch = fa.epoch;
-  p.f.out = fa.out;
-  p.f.ldo = fa.ldo;
-  PeerMaps pm{};
-  for (int k = 0; k < fa.world; ++k) {
-    rc = make_tmap(&pm.m[k], dtype, fa.peer_parts[k], M, N, N, fa.world == 8 ? 64 : 128, false, /*swizzle=*/false);
-    if (rc != TBIK_OK) return rc;
-  }
-  const int grid = pl.grid + comm;
-  if (dtype == TBIK_DTYPE_BF16) return launch<__nv_bfloat16, 256, 3, 1, false, true>(ta, tb, tc, p, grid, stream, &pm);
-  return launch<__half, 256, 3, 1, false, true>(ta, tb, tc, p, grid, stream, &pm);
+    return set_error(TBIK_ERR_DTYPE, "tbik_gemm supports bf16 and fp16 operands");
+  if (node_dtype != TBIK_NODE_INPUT)
+    return set_error(TBIK_ERR_DTYPE, "tbik_gemm: only node_dtype = TBIK_NODE_INPUT is implemented");
+  if (M < 0 || N < 0 || K <= 0) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: M, N must be >= 0 and K > 0");
+  if (leaf <= 0 || leaf % BK != 0) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: leaf must be a positive multiple of 64");
+  if (tiling < 0 || tiling > 6) return set_error(TBIK_ERR_ARG, "tbik_gemm: tiling must be 0..6");
+  if (tree_shape(K, leaf, T, F, L) != TBIK_OK)
+    return set_error(TBIK_ERR_SHAPE, "tbik_gemm: K must be a multiple of the leaf width");
+  if (*L > 16) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: reduction tree deeper than 16 levels is not supported");
+  if (M == 0 || N == 0) return TBIK_OK;
+  if (!A || !W || !C) return set_error(TBIK_ERR_ARG, "tbik_gemm: null pointer");
+  if (lda < K || ldw < K || ldc < N) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: leading dimension smaller than the row");
+  if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(W) & 15u) || (lda % 8) || (ldw % 8))
+    return set_error(TBIK_ERR_ALIGN, "tbik_gemm: A and W must be 16-byte aligned with row strides that are multiples of 8 elements");
+  if (reinterpret_cast<uintptr_t>(C) & 1u) return set_error(TBIK_ERR_ALIGN, "tbik_gemm: C must be 2-byte aligned");
+  if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 15u))
+    return set_error(TBIK_ERR_ALIGN, "tbik_gemm: workspace must be 16-byte aligned");
+  return TBIK_OK;
 }
 
-size_t gemm_fused_workspace_bytes(int M, int N, int64_t K, int leaf) {
+int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
+                int dtype, int leaf, int node_dtype, int max_ctas, int tiling, void* workspace, size_t ws_bytes,
+                cudaStream_t stream, int splits) {
   int T, F, L;
-  if (M <= 0 || N <= 0 || tree_shape(K, leaf, &T, &F, &L) != TBIK_OK) return 0;
-  return make_plan(3, M, N, L, 0).scratch_bytes;
+  int rc = gemm_check_args(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, tiling, workspace, &T, &F, &L);
+  if (rc != TBIK_OK || M == 0 || N == 0) return rc;
+  const bool have_ws = workspace != nullptr && ws_bytes > 0;
+
+  // splits: 0 = automatic (only together with tiling 0), 1 = none, else a power of two of whole subtrees
+  if (splits < 0 || splits > kMaxSplits || (splits & (splits - 1)) != 0)
+    return set_error(TBIK_ERR_ARG, "tbik_gemm: the number of K-slabs must be a power of two up to 16");
+  if (splits > 1 && (tiling == 0 || splits > T / F))
+    return set_error(TBIK_ERR_SHAPE, "tbik_gemm: K-slabs need an explicit tiling and at most T / F slabs (whole subtrees)");
+  const Plan pl = tiling == 0 ? auto_plan(M, N, L, splits == 1 ? 1 : T / F, T * (leaf / BK), max_ctas, ws_bytes, have_ws)
+                              : make_plan(tiling, M, N, L, max_ctas, splits > 1 ? splits : 1);
+  if (!pl.valid) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: too many output tiles for K-slabs");
+  if (pl.total_bytes() > 0 && (!have_ws || pl.total_bytes() > ws_bytes)) {
+    char msg[200];
+    snprintf(msg, sizeof(msg),
+             "tbik_gemm: a reduction tree of %d levels needs %zu bytes of scratch for this tiling (got %zu); "
+             "see tbik_gemm_workspace_bytes", L, pl.total_bytes(), have_ws ? ws_bytes : size_t(0));
+    return set_error(TBIK_ERR_SHAPE, msg);
+  }
+  return gemm_launch_plan(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, T, F, pl, workspace, stream);
 }
 
 // ---------------------------------------------------------------- the entry point that allocates nothing
-// Scratch for the upper stack levels, built into the library image: every GPU that loads the library
-// holds these bytes until the process exits.  32 MiB covers every schedule the automatic choice picks
-// for a Qwen3-8B row-split layer (the K-slab roots of a decode-sized call are under 10 MiB) and the
-// 128x256 tiling of its deepest tree (down_proj, 5 levels: 148 CTAs x 3 levels x 64 KiB = 27.75 MiB).
+// Scratch for the upper stack levels, the K-slab roots and their arrival counters, built into the library image:
+// every GPU that loads the library holds these bytes until the process exits.  32 MiB covers every schedule the
+// automatic choice picks for a Qwen3-8B row-split layer (the K-slab roots of a decode-sized call are under
+// 10 MiB) and the 128x256 tiling of its deepest tree (down_proj, 5 levels: 148 CTAs x 3 levels x 64 KiB =
+// 27.75 MiB).  The array is zero when the module is loaded, which is the state the arrival counters need, and
+// every call that completes leaves them zero again.
 constexpr size_t kStaticScratchBytes = size_t(32) << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 size_t gemm_static_scratch_bytes() { return kStaticScratchBytes; }
 
+// The schedule the automatic choice prefers, if its scratch fits the array; else the best one that fits --
+// unless that would mean falling back from a full-rate tiling to the narrow decode tilings, which need no
+// scratch at any size but would run a large problem several times slower without saying so.
+static bool static_plan(int M, int N, int T, int F, int L, int leaf, Plan* out, size_t* want_bytes) {
+  const Plan want = auto_plan(M, N, L, T / F, T * (leaf / BK), 0, ~size_t(0), true);
+  *want_bytes = want.total_bytes();
+  const Plan pl = want.total_bytes() <= kStaticScratchBytes
+                      ? want
+                      : auto_plan(M, N, L, T / F, T * (leaf / BK), 0, kStaticScratchBytes, true);
+  const bool degraded = pl.tiling >= 5 && want.tiling < 5;
+  if (!pl.valid || pl.total_bytes() > kStaticScratchBytes || degraded) return false;
+  *out = pl;
+  return true;
+}
+
+int gemm_static_accepts(int M, int N, int64_t K, int leaf) {
+  int T, F, L;
+  if (M <= 0 || N <= 0 || tree_shape(K, leaf, &T, &F, &L) != TBIK_OK || L > 16) return 0;
+  Plan pl{};
+  size_t want = 0;
+  return static_plan(M, N, T, F, L, leaf, &pl, &want) ? 1 : 0;
+}
+
 int gemm_launch_static(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw,
                        int64_t ldc, int dtype, int leaf, int node_dtype, cudaStream_t stream) {
   // In host code `g_static_scratch` is only a handle for the runtime, not a device address: the address
   // the kernel may use has to be asked for, once per device, with that device current.
-  static void* device_addr[64] = {};
+  static std::atomic<void*> device_addr[kMaxDevices];
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return set_cuda_error(e, "cudaGetDevice");
-  if (dev < 0 || dev >= 64) return set_error(TBIK_ERR_ARG, "tbik_gemm_static: device index out of range");
-  if (device_addr[dev] == nullptr) {
-    void* addr = nullptr;
-    e = cudaGetSymbolAddress(&addr, g_static_scratch);
-    if (e != cudaSuccess || addr == nullptr) return set_cuda_error(e, "cudaGetSymbolAddress(g_static_scratch)");
-    device_addr[dev] = addr;
+  if (dev < 0 || dev >= kMaxDevices) return set_error(TBIK_ERR_ARG, "tbik_gemm_static: device index out of range");
+  void* scratch = device_addr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
+    e = cudaGetSymbolAddress(&scratch, g_static_scratch);
+    if (e != cudaSuccess || scratch == nullptr) return set_cuda_error(e, "cudaGetSymbolAddress(g_static_scratch)");
+    device_addr[dev].store(scratch, std::memory_order_release);  // two racing first calls store the same address
   }
-  const size_t need = gemm_workspace_bytes(M, N, K, leaf);
-  if (need > kStaticScratchBytes) {
-    char msg[200];
+  int T, F, L;
+  int rc = gemm_check_args(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, 0, nullptr, &T, &F, &L);
+  if (rc != TBIK_OK || M == 0 || N == 0) return rc;
+  Plan pl{};
+  size_t want_bytes = 0;
+  if (!static_plan(M, N, T, F, L, leaf, &pl, &want_bytes)) {
+    char msg[240];
     snprintf(msg, sizeof(msg),
              "tbik_gemm_static: these sizes need %zu bytes of scratch, more than the %zu bytes built into the "
-             "library; use tbik_gemm_ws with a caller-owned buffer", need, kStaticScratchBytes);
+             "library; use tbik_gemm_ws with a caller-owned buffer", want_bytes, kStaticScratchBytes);
     return set_error(TBIK_ERR_SHAPE, msg);
   }
-  return gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, 0, 0, device_addr[dev],
-                     kStaticScratchBytes, stream, 0);
+  return gemm_launch_plan(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, T, F, pl, scratch, stream);
 }
 
 int gemm_status(uint32_t out[4]) {

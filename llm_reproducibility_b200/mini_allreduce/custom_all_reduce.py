@@ -143,10 +143,18 @@ class CustomAllreduce:
 
     @staticmethod
     def free_shared_buffer(pointers: List[int], group: Optional[ProcessGroup] = None) -> None:
+        """Unmap the peers' copies, then free this rank's own allocation."""
         if not dist.is_available() or not dist.is_initialized():
             return
         rank = dist.get_rank(group=group)
-        CudaRTLibrary().cudaFree(ctypes.c_void_p(pointers[rank]))
+        lib = CudaRTLibrary()
+        for i, p in enumerate(pointers):
+            if i != rank:
+                try:
+                    lib.cudaIpcCloseMemHandle(ctypes.c_void_p(p))
+                except RuntimeError as exc:  # the owner is gone already: nothing left to unmap
+                    logger.debug("cudaIpcCloseMemHandle: %s", exc)
+        lib.cudaFree(ctypes.c_void_p(pointers[rank]))
 
     @contextmanager
     def capture(self):
@@ -276,20 +284,3 @@ class CustomTreeAllreduce(CustomAllreduce):
 
     def custom_tree_all_reduce(self, input: torch.Tensor) -> Optional[torch.Tensor]:
         return self._dispatch(input)
-
-    def matmul_tree_all_reduce(self, A: torch.Tensor, B: torch.Tensor, comm_ctas: int = 0) -> Optional[torch.Tensor]:
-        """tree-all-reduce(A @ B) in one kernel launch: a few CTAs of the GEMM grid reduce and gather finished
-        output tiles over NVLink while the others keep multiplying.  Returns None when this path cannot take
-        the call (communicator disabled, a single rank, sizes, graph capture); the caller then composes
-        `matmul_tp_persistent` and `custom_tree_all_reduce`, which gives the same bits."""
-        if self.disabled or self.world_size not in (2, 4, 8) or self._IS_CAPTURING:
-            return None
-        if A.dtype not in (torch.bfloat16, torch.float16) or A.dim() != 2 or B.dim() != 2:
-            return None
-        M, N = A.shape[0], B.shape[1]
-        nbytes = M * N * A.element_size()
-        if M == 0 or N % 8 != 0 or nbytes >= self.max_size or not (self.world_size == 2 or self.full_nvlink):
-            return None
-        if A.is_cuda and torch.cuda.is_current_stream_capturing():
-            return None
-        return ops.tree_matmul_allreduce(self._ptr, A, B, self.buffer_ptrs[self.rank], self.max_size, comm_ctas)

@@ -55,12 +55,6 @@ def register_graph_buffers(fa: int, handles: List[List[int]], offsets: List[List
     _custom_ar.register_graph_buffers(fa, handles, offsets)
 
 
-def tree_matmul_allreduce(fa: int, A: torch.Tensor, B: torch.Tensor, reg_buffer: int, reg_buffer_sz_bytes: int,
-                          comm_ctas: int = 0) -> torch.Tensor:
-    """Row-split GEMM and tree all-reduce in one kernel launch (addition of this implementation)."""
-    return _custom_ar.tree_matmul_allreduce(fa, A, B, reg_buffer, reg_buffer_sz_bytes, comm_ctas)
-
-
 def tree_all_reduce_within(fa: int, reg_base: int, byte_offset: int, out: torch.Tensor) -> None:
     """Tree all-reduce of a message a producer wrote in place inside a registered buffer (addition)."""
     _custom_ar.tree_all_reduce_within(fa, reg_base, byte_offset, out)

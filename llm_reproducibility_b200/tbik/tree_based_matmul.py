@@ -42,13 +42,14 @@ _WORKSPACES = {}  # (device index, stream) -> uint8 tensor; scratch for the uppe
 
 
 def _workspace(device: torch.device, stream: int, nbytes: int) -> Optional[torch.Tensor]:
-    """Scratch buffer for one (device, stream); grown on demand, never shared between streams."""
+    """Scratch buffer for one (device, stream); grown on demand, never shared between streams.  Allocated
+    zero-filled: the arrival counters at its head must start at zero, and every call leaves them zero."""
     if nbytes == 0:
         return None
     key = (device.index, stream)
     ws = _WORKSPACES.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        ws = torch.zeros(nbytes, dtype=torch.uint8, device=device)
         _WORKSPACES[key] = ws
     return ws
 

@@ -151,31 +151,6 @@ def _trace(fa: int) -> List[int]:
     return [int(v) for v in buf[: 8 * n.value]]
 
 
-def _tree_matmul_allreduce(fa: int, A: torch.Tensor, B: torch.Tensor, reg_buffer: int, reg_buffer_sz_bytes: int,
-                           comm_ctas: int = 0) -> torch.Tensor:
-    """out = tree all-reduce over ranks of (A @ B), one kernel launch (tbik_ar_gemm_tree_allreduce)."""
-    from ..tbik.tree_based_matmul import _DTYPE_CODE as GEMM_DTYPES, _LEAF, _workspace, prepare_operands
-    import os
-    if A.dtype not in GEMM_DTYPES or B.dtype != A.dtype:
-        raise RuntimeError("tree_matmul_allreduce supports bfloat16 and float16")
-    M, K = A.shape
-    N = B.shape[1]
-    leaf = int(os.environ.get("TBIK_LEAF", _LEAF[A.dtype]))
-    A2, W = prepare_operands(A, B)
-    out = torch.empty((M, N), device=A.device, dtype=A.dtype)
-    with torch.cuda.device(A.device):
-        stream = _stream_of(A)
-        L = _lib.lib()
-        ws = _workspace(A.device, stream, int(L.tbik_ar_gemm_workspace_bytes(M, N, K, leaf)))
-        rc = L.tbik_ar_gemm_tree_allreduce(fa, A2.data_ptr(), W.data_ptr(), out.data_ptr(), M, N, K,
-                                           max(A2.stride(0), K), max(W.stride(0), K), N, GEMM_DTYPES[A.dtype], leaf,
-                                           reg_buffer, reg_buffer_sz_bytes,
-                                           ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
-                                           comm_ctas, stream)
-    _lib.check(rc, "tbik_ar_gemm_tree_allreduce")
-    return out
-
-
 def _tree_matmul(A: torch.Tensor, B: torch.Tensor, bias=None) -> torch.Tensor:
     from ..tbik.tree_based_matmul import matmul_tp_persistent
     return matmul_tp_persistent(A, B, bias)
@@ -216,9 +191,6 @@ def _register() -> None:
     lib.impl("tree_all_reduce_within", _tree_all_reduce_within, "CUDA")
     lib.define("trace(int fa) -> int[]")
     lib.impl("trace", _trace, any_key)
-    lib.define("tree_matmul_allreduce(int fa, Tensor A, Tensor B, int reg_buffer, int reg_buffer_sz_bytes, "
-               "int comm_ctas=0) -> Tensor")
-    lib.impl("tree_matmul_allreduce", _tree_matmul_allreduce, "CUDA")
     lib.define("tree_matmul(Tensor A, Tensor B, Tensor? bias=None) -> Tensor")
     lib.impl("tree_matmul", _tree_matmul, "CUDA")
     _LIBRARY = lib  # keep alive
@@ -258,10 +230,6 @@ def register_graph_buffers(*args, **kwargs):
 
 def meta_size(*args, **kwargs):
     return torch.ops.tbik_kernel.meta_size.default(*args, **kwargs)
-
-
-def tree_matmul_allreduce(*args, **kwargs):
-    return torch.ops.tbik_kernel.tree_matmul_allreduce.default(*args, **kwargs)
 
 
 def tree_all_reduce_within(*args, **kwargs):

@@ -32,13 +32,21 @@ def tree_allreduce_parity(rank, world, cases, max_size):
     for (numel, dtype, seed) in cases:
         xs = _inputs(world, numel, dtype, seed, device)
         want = tree_allreduce_ref(xs)
-        for mode, one_max, push_min, chunks in (("auto", 0, 0, 0), ("oneshot", 1 << 40, 0, 0), ("twoshot", 1, 1 << 60, 0),
-                                                ("push", 1, 1, 0), ("push1", 1, 1, 1), ("push7", 1, 1, 7)):
-            if mode == "oneshot" and numel * xs[0].element_size() > (8 << 20):
+        # (name, one-shot limit, push from, push chunks, packs per access, packs in flight per thread, threads)
+        for mode, one_max, push_min, chunks, vec, loads, threads in (
+                ("auto", 0, 0, 0, 0, 0, 0), ("oneshot", 1 << 40, 0, 0, 0, 0, 0), ("twoshot", 1, 1 << 60, 0, 0, 0, 0),
+                ("push", 1, 1, 0, 0, 0, 0), ("push1", 1, 1, 1, 0, 0, 0), ("push7", 1, 1, 7, 0, 0, 0),
+                ("oneshot-256bit", 1 << 40, 0, 0, 2, 0, 0), ("twoshot-256bit", 1, 1 << 60, 0, 2, 0, 0),
+                ("push1-256bit", 1, 1, 1, 2, 0, 0), ("twoshot-deep", 1, 1 << 60, 0, 1, 32, 0),
+                ("oneshot-deep-256bit", 1 << 40, 0, 0, 2, 32, 0), ("twoshot-shallow", 1, 1 << 60, 0, 1, 4, 256)):
+            if mode.startswith("oneshot") and numel * xs[0].element_size() > (8 << 20):
                 continue
             ops.configure(ar._ptr, ops.CFG_ONESHOT_MAX_BYTES, one_max)
             ops.configure(ar._ptr, ops.CFG_PUSH_MIN_BYTES, push_min)
             ops.configure(ar._ptr, ops.CFG_PUSH_CHUNKS, chunks)
+            ops.configure(ar._ptr, ops.CFG_VEC_PACKS, vec)
+            ops.configure(ar._ptr, ops.CFG_LOADS_IN_FLIGHT, loads)
+            ops.configure(ar._ptr, ops.CFG_THREADS, threads)
             got = ar.custom_tree_all_reduce(xs[rank])
             assert got is not None, (numel, dtype)
             torch.cuda.synchronize()
@@ -46,6 +54,9 @@ def tree_allreduce_parity(rank, world, cases, max_size):
             ok = torch.equal(bits(got), bits(want))
             report.append((numel, str(dtype), mode, ok))
             assert ok, f"rank {rank}: tree all-reduce differs from oracle: numel={numel} {dtype} {mode}"
+        ops.configure(ar._ptr, ops.CFG_VEC_PACKS, 0)
+        ops.configure(ar._ptr, ops.CFG_LOADS_IN_FLIGHT, 0)
+        ops.configure(ar._ptr, ops.CFG_THREADS, 0)
         ops.configure(ar._ptr, ops.CFG_ONESHOT_MAX_BYTES, 0)
         ops.configure(ar._ptr, ops.CFG_PUSH_MIN_BYTES, 0)
         ops.configure(ar._ptr, ops.CFG_PUSH_CHUNKS, 0)
@@ -169,7 +180,7 @@ def dispatcher(rank, world):
     full = matmul_tp_persistent(X, W.t())
     torch.cuda.synchronize()
     assert torch.equal(bits(out), bits(full)), "TP result differs from the single-device result"
-    # the un-fused composition gives the same bits, repeatedly (the registered buffer is reused)
+    # GEMM then all-reduce as two calls gives the same bits, repeatedly (the registered buffer is reused)
     for _ in range(3):
         part = matmul_tp_persistent(X[:, rank * ks:(rank + 1) * ks], Layer.weight.t())
         assert torch.equal(bits(tar.tree_all_reduce_sum(part, None)), bits(full))
@@ -184,27 +195,129 @@ def dispatcher(rank, world):
         want = matmul_tp_persistent(X2, W2.t())
         torch.cuda.synchronize()
         assert torch.equal(bits(got), bits(want)), (K2, N2)
-        # the fused kernel against the two-kernel composition, and with other comm-CTA counts
-        os.environ["TBIK_FUSED"] = "1"
-        fused = tar.tree_matmul_all_reduce(X2[:, rank * k2:(rank + 1) * k2], W2[:, rank * k2:(rank + 1) * k2].t(), None)
-        os.environ["TBIK_FUSED"] = "0"
-        assert torch.equal(bits(fused), bits(want))
-        for cc in (2, 8, 40):
-            y = tar.custom_ar.matmul_tree_all_reduce(X2[:, rank * k2:(rank + 1) * k2], W2[:, rank * k2:(rank + 1) * k2].t(), cc)
-            torch.cuda.synchronize()
-            tar.custom_ar.check_status()
-            assert y is not None and torch.equal(bits(y), bits(want)), (K2, N2, cc)
-    # ragged sizes through the fused kernel (edge tiles in M and N), repeated calls reuse the tile flags
+    # ragged sizes (edge tiles in M and N; the registered buffer is reused call after call)
     g3 = torch.Generator(device=device).manual_seed(5)
     X3 = torch.randn(300, 2048, generator=g3, device=device).to(torch.bfloat16)
     W3 = (torch.randn(520, 2048, generator=g3, device=device) * 0.05).to(torch.bfloat16)
     k3 = 2048 // world
     want3 = matmul_tp_persistent(X3, W3.t())
     for _ in range(4):
-        y = tar.custom_ar.matmul_tree_all_reduce(X3[:, rank * k3:(rank + 1) * k3], W3[:, rank * k3:(rank + 1) * k3].t())
+        y = tar.tree_matmul_all_reduce(X3[:, rank * k3:(rank + 1) * k3], W3[:, rank * k3:(rank + 1) * k3].t(), None)
         torch.cuda.synchronize()
-        assert y is not None and torch.equal(bits(y), bits(want3))
+        assert torch.equal(bits(y), bits(want3))
+    # under a CUDA graph the GEMM writes into the registered buffer too (no staging copy, no late registration)
+    Xs, Ws = X3[:, rank * k3:(rank + 1) * k3].contiguous(), W3[:, rank * k3:(rank + 1) * k3].contiguous()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            yg = tar.tree_matmul_all_reduce(Xs, Ws.t(), None)
+    torch.cuda.current_stream().wait_stream(stream)
+    dist.barrier()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(bits(yg), bits(want3))
     tar.custom_ar.check_status()
+    dist.barrier()
+    tar.reset_communicator()
+    return True
+
+
+def barrier_timeout(rank, world):
+    """A cross-GPU wait that runs out: rank 0 enters a collective that no peer joins.  Its kernel must give up
+    after the configured limit and return (nothing hangs, nothing faults), the status record must name the
+    barrier, the communicator must refuse further use, close() must work, and a rebuilt one must be correct."""
+    from llm_reproducibility_b200.mini_allreduce import CustomTreeAllreduce
+    from llm_reproducibility_b200.mini_allreduce import custom_all_reduce_ops as ops
+    from oracle.tbik_ref import tree_allreduce_ref
+    import time
+
+    device = torch.device(f"cuda:{rank}")
+    gloo = dist.new_group(backend="gloo")
+    ar = CustomTreeAllreduce(group=gloo, device=device, max_size=4 << 20)
+    assert not ar.disabled
+    xs = _inputs(world, 1 << 16, torch.bfloat16, 21, device)
+    want = tree_allreduce_ref(xs)
+    got = ar.custom_tree_all_reduce(xs[rank])
+    torch.cuda.synchronize()
+    assert torch.equal(bits(got), bits(want))
+    ops.configure(ar._ptr, ops.CFG_WAIT_LIMIT_NS, 20_000_000)  # 20 ms
+    dist.barrier(group=gloo)  # every rank is idle: no kernel in flight anywhere
+    elapsed = None
+    if rank == 0:
+        t0 = time.perf_counter()
+        lonely = ar.custom_tree_all_reduce(xs[rank])  # the peers skip this call
+        torch.cuda.synchronize()                      # returns: the kernel gave up on its first barrier
+        elapsed = time.perf_counter() - t0
+        assert lonely is not None and elapsed < 1.0, elapsed
+        st = ops.status(ar._ptr)
+        assert st[0] == 1 and st[1] == 0 and 1 <= st[3] < world and st[6] == 1, st
+        try:
+            ar.check_status()
+            raise AssertionError("check_status must raise after a timeout")
+        except RuntimeError as e:
+            assert "timed out" in str(e)
+        try:
+            ar.custom_tree_all_reduce(xs[rank])
+            raise AssertionError("a communicator whose kernel timed out must refuse further calls")
+        except RuntimeError as e:
+            assert "(-7)" in str(e), str(e)
+    dist.barrier(group=gloo)
+    ar.close()
+    dist.barrier(group=gloo)
+    # a fresh communicator on the same GPUs works
+    ar2 = CustomTreeAllreduce(group=gloo, device=device, max_size=4 << 20)
+    assert not ar2.disabled
+    for _ in range(3):
+        got = ar2.custom_tree_all_reduce(xs[rank])
+    torch.cuda.synchronize()
+    ar2.check_status()
+    assert torch.equal(bits(got), bits(want))
+    dist.barrier(group=gloo)
+    ar2.close()
+    return elapsed if rank == 0 else True
+
+
+def pipelined_layer(rank, world):
+    """Row-block pipeline of tree_matmul_all_reduce (GEMM of block i+1 beside the all-reduce of block i on a second
+    stream) against the single-device result, bit for bit; phase stamps of the all-reduce are sane."""
+    from llm_reproducibility_b200.mini_allreduce import custom_all_reduce_ops as ops
+    from llm_reproducibility_b200.tbik import tree_based_all_reduce as tar
+    from llm_reproducibility_b200.tbik.tree_based_matmul import matmul_tp_persistent
+
+    device = torch.device(f"cuda:{rank}")
+    os.environ["TBIK_PIPELINE"] = "1"
+    g = torch.Generator(device=device).manual_seed(4321)
+    for (M, K, N) in ((4096, 4096, 4096), (4096 + 300, 2048, 1024), (8192, 2048, 2048)):
+        X = torch.randn(M, K, generator=g, device=device).to(torch.bfloat16)
+        W = (torch.randn(N, K, generator=g, device=device) * 0.02).to(torch.bfloat16)
+        ks = K // world
+        Xr, Wr = X[:, rank * ks:(rank + 1) * ks], W[:, rank * ks:(rank + 1) * ks]
+        assert tar._pipeline_blocks(M, N, ks, world) >= 2
+        want = matmul_tp_persistent(X, W.t())
+        for _ in range(3):
+            got = tar.tree_matmul_all_reduce(Xr, Wr.t(), None)
+        torch.cuda.synchronize()
+        tar.custom_ar.check_status()
+        assert torch.equal(bits(got), bits(want)), (M, K, N)
+        os.environ["TBIK_PIPELINE"] = "0"
+        plain = tar.tree_matmul_all_reduce(Xr, Wr.t(), None)
+        os.environ["TBIK_PIPELINE"] = "1"
+        assert torch.equal(bits(plain), bits(want)), (M, K, N)
+    # phase stamps: entry <= after the first barrier <= after the reduce phase <= exit, for every CTA
+    ar = tar.custom_ar
+    ops.configure(ar._ptr, ops.CFG_TRACE, 1)
+    x = torch.randn(1 << 22, generator=g, device=device).to(torch.bfloat16)
+    ar.custom_tree_all_reduce(x)
+    torch.cuda.synchronize()
+    tr = ops.trace(ar._ptr)
+    assert len(tr) >= 8 and len(tr) % 8 == 0
+    for b in range(len(tr) // 8):
+        t = tr[8 * b: 8 * b + 8]
+        assert 0 < t[0] <= t[1] <= t[2] <= t[4], t
+    ops.configure(ar._ptr, ops.CFG_TRACE, 0)
     dist.barrier()
     tar.reset_communicator()
     return True

@@ -55,6 +55,9 @@ class FakeCudaRT:
         shm = shared_memory.SharedMemory(name=handle.name)
         return ctypes.c_void_p(self._new_addr(shm))
 
+    def cudaIpcCloseMemHandle(self, ptr):
+        self.cudaFree(ptr)
+
     def cudaFree(self, ptr):
         shm = self.segments.pop(ptr.value)
         shm.close()
@@ -149,13 +152,6 @@ class FakeOps:
 
     def all_reduce(self, fa, inp, out, reg_buffer, reg_sz):
         self._reduce(fa, inp, out, reg_buffer, reg_sz, False)
-
-    def tree_matmul_allreduce(self, fa, A, B, reg_buffer, reg_sz, comm_ctas=0):
-        from oracle.tbik_ref import tbik_matmul_ref
-        part = tbik_matmul_ref(A, B)
-        out = torch.empty_like(part)
-        self._reduce(fa, part, out, reg_buffer, reg_sz, True)
-        return out
 
     def dispose(self, fa):
         self.comms.pop(fa)

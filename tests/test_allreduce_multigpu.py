@@ -46,3 +46,16 @@ def test_graph_capture_registers_buffers():
 @needs_multi
 def test_dispatcher_and_row_parallel_layer():
     assert all(run_ranks(w.dispatcher, _world(), backend="nccl"))
+
+
+@needs_multi
+def test_pipelined_row_blocks_match_single_device():
+    assert all(run_ranks(w.pipelined_layer, _world(), backend="nccl"))
+
+
+@needs_multi
+def test_a_wait_that_runs_out_returns_and_reports():
+    """No GPU hangs or faults here: the lonely kernel's bounded wait (20 ms) expires, it writes a status record
+    and returns; the peers are idle on the host meanwhile."""
+    reports = run_ranks(w.barrier_timeout, _world(), backend="nccl")
+    assert reports[0] < 1.0
