@@ -598,8 +598,9 @@ def main():
         # kernels of this repository per step: one GEMM per layer, or per row block of a layer one GEMM and one
         # all-reduce when the layer is pipelined over row blocks
         if tp > 1:
-            from llm_reproducibility_b200.tbik.tree_based_all_reduce import _pipeline_blocks
-            launches_per_step = sum(2 * _pipeline_blocks(M, N, K // tp, tp) for _, K, N in LAYERS)
+            from llm_reproducibility_b200.tbik.tree_based_all_reduce import _pipeline_plan
+            plans = [_pipeline_plan(M, N, K // tp, tp) for _, K, N in LAYERS]
+            launches_per_step = sum(2 * (len(pl[0]) if pl else 1) for pl in plans)
         else:
             launches_per_step = len(LAYERS)
         line = {

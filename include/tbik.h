@@ -97,6 +97,12 @@ int tbik_gemm_slabs(const void* A, const void* W, void* C, int M, int N, int K, 
                     int dtype, int leaf, int node_dtype, int tiling, int slabs, void* workspace, size_t workspace_bytes,
                     tbik_stream_t stream);
 
+/* The schedule tbik_gemm_ws would run for these sizes on the current device with `workspace_bytes` of scratch and
+ * at most `max_ctas` CTAs (0 = one per SM): out[0] = tiling (codes of tbik_gemm_ex), out[1] = K-slabs, out[2] = CTAs,
+ * out[3] = 1 if the variant with the deeper on-chip stack is used.  A function of the sizes only; nothing is
+ * launched.  Without a visible GPU it answers for 148 SMs.  No counterpart in the reference. */
+int tbik_gemm_plan(int M, int N, int64_t K, int leaf, int max_ctas, size_t workspace_bytes, int out[4]);
+
 /* As tbik_gemm_ws, with the schedule exposed: at most `max_ctas` CTAs (0 = one per SM) and
  * `tiling` 0 = automatic, 1 = 128x128 tile per CTA, 2 = 256x128 per CTA pair, 3 = 128x256 per CTA,
  * 4 = 256x256 per CTA pair, 5 = 128x64 per CTA, 6 = 128x32 per CTA (an explicit tiling runs without K-slabs).
@@ -153,6 +159,7 @@ typedef void* tbik_ar_t;
 #define TBIK_AR_CFG_PUSH_CHUNKS 7       /* chunks the push schedule cuts a message into, 1..64 (0 = built-in) */
 #define TBIK_AR_CFG_VEC_PACKS 8         /* 16-byte packs per load / store instruction: 1, or 2 = 256-bit accesses (0 = built-in) */
 #define TBIK_AR_CFG_LOADS_IN_FLIGHT 9   /* 16-byte packs a thread requests before it uses the first, 1..32 (0 = built-in) */
+#define TBIK_AR_CFG_CLUSTER_PAIRS 11     /* 1 (default): CTAs are launched as clusters of two, so that beside a GEMM made of CTA pairs the all-reduce takes whole SM pairs; 0: plain launch */
 #define TBIK_AR_CFG_TRACE 10            /* 1: every launch records per-CTA phase time stamps (tbik_ar_trace); 0: off      */
 
 /* Size in bytes of the signal (flag) area at the start of every rank's meta buffer.
@@ -196,6 +203,23 @@ int tbik_ar_tree_allreduce(tbik_ar_t comm, const void* inp, void* out, int64_t n
  * Replaces: the same reference functions as tbik_ar_tree_allreduce, minus the copy at custom_all_reduce.cu:112-114. */
 int tbik_ar_tree_allreduce_within(tbik_ar_t comm, const void* reg_base, size_t byte_offset, void* out, int64_t numel,
                                   int dtype, tbik_stream_t stream);
+
+/* The row-split layer as a pipeline: out[M, N] (contiguous) = tree-all-reduce over ranks of (A * W^T), computed
+ * block of rows by block of rows.  Block i's GEMM (tbik_gemm_ws arithmetic) writes its partial rows into the
+ * registered buffer at reg_base on `main_stream`; its tree all-reduce runs on `side_stream` with at most
+ * `comm_ctas` CTAs while the GEMM of block i + 1 occupies the other SMs; the layer's last all-reduce gets the
+ * whole GPU.  The call enqueues everything (kernels, event records and waits) and returns; `main_stream` ends
+ * up waiting for the last all-reduce, so work enqueued on it afterwards sees the complete result.  Cutting
+ * the rows into blocks cannot change a bit: no sum ever joins two rows.  block_rows[0 .. num_blocks) are the
+ * rows of each block (they add up to M; multiples of 256 keep the GEMM tiles whole; a short last block keeps the
+ * one all-reduce that nothing hides short).  Collective: every rank calls it in the same order with the same sizes.  Not
+ * for use under stream capture.
+ * Replaces: the sequence matmul_tp_persistent -> tree_all_reduce_sum in the patched forward,
+ *           src/patch/patch_tp_invariant.py:31-34 (and the staging copy at custom_all_reduce.cu:112-114). */
+int tbik_ar_row_split_layer(tbik_ar_t comm, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
+                            int64_t ldw, int dtype, int leaf, void* reg_base, size_t reg_bytes, void* workspace,
+                            size_t workspace_bytes, const int* block_rows, int num_blocks, int comm_ctas,
+                            tbik_stream_t main_stream, tbik_stream_t side_stream);
 
 /* As above with the non-tree arithmetic: fp32 accumulation in rank order, one final rounding.
  * Replaces: all_reduce, custom_all_reduce.cu:57-98 / allreduce, custom_all_reduce.cuh:462-521. */

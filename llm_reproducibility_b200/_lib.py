@@ -27,6 +27,7 @@ _PROTOTYPES = {
     "tbik_gemm": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _vp]),
     "tbik_gemm_workspace_bytes": (_sz, [_i32, _i32, _i64, _i32]),
     "tbik_gemm_ws": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _vp, _sz, _vp]),
+    "tbik_gemm_plan": (_i32, [_i32, _i32, _i64, _i32, _i32, _sz, ctypes.POINTER(_i32)]),
     "tbik_gemm_ex": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "tbik_gemm_slabs_workspace_bytes": (_sz, [_i32, _i32, _i64, _i32, _i32, _i32]),
     "tbik_gemm_slabs": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
@@ -42,6 +43,8 @@ _PROTOTYPES = {
     "tbik_ar_tree_allreduce": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp, _sz, _vp]),
     "tbik_ar_allreduce": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp, _sz, _vp]),
     "tbik_ar_tree_allreduce_within": (_i32, [_vp, _vp, _sz, _vp, _i64, _i32, _vp]),
+    "tbik_ar_row_split_layer": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i32, _i32, _vp, _sz, _vp, _sz,
+                                        ctypes.POINTER(_i32), _i32, _i32, _vp, _vp]),
     "tbik_ar_trace": (_i32, [_vp, ctypes.POINTER(ctypes.c_uint64), _i32, ctypes.POINTER(_i32)]),
     "tbik_ar_graph_meta_count": (_i32, [_vp, ctypes.POINTER(_i32)]),
     "tbik_ar_graph_meta": (_i32, [_vp, _vp, ctypes.POINTER(_i64)]),

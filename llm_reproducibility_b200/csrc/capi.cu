@@ -54,6 +54,11 @@ int tbik_gemm_ex(const void* A, const void* W, void* C, int M, int N, int K, int
                            workspace_bytes, static_cast<cudaStream_t>(stream), tiling == 0 ? 0 : 1);
 }
 
+int tbik_gemm_plan(int M, int N, int64_t K, int leaf, int max_ctas, size_t workspace_bytes, int out[4]) {
+  if (!out) return tbik::set_error(TBIK_ERR_ARG, "tbik_gemm_plan: null output pointer");
+  return tbik::gemm_plan_query(M, N, K, leaf, max_ctas, workspace_bytes, out);
+}
+
 size_t tbik_gemm_slabs_workspace_bytes(int M, int N, int64_t K, int leaf, int tiling, int slabs) {
   return tbik::gemm_split_workspace_bytes(M, N, K, leaf, tiling, slabs);
 }
@@ -111,6 +116,15 @@ int tbik_ar_allreduce(tbik_ar_t comm, const void* inp, void* out, int64_t numel,
 int tbik_ar_tree_allreduce_within(tbik_ar_t comm, const void* reg_base, size_t byte_offset, void* out, int64_t numel,
                                   int dtype, tbik_stream_t stream) {
   return tbik::ar_run_within(comm, reg_base, byte_offset, out, numel, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int tbik_ar_row_split_layer(tbik_ar_t comm, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
+                            int64_t ldw, int dtype, int leaf, void* reg_base, size_t reg_bytes, void* workspace,
+                            size_t workspace_bytes, const int* block_rows, int num_blocks, int comm_ctas,
+                            tbik_stream_t main_stream, tbik_stream_t side_stream) {
+  return tbik::ar_row_split_layer(comm, A, W, out, M, N, K, lda, ldw, dtype, leaf, reg_base, reg_bytes, workspace,
+                                  workspace_bytes, block_rows, num_blocks, comm_ctas, static_cast<cudaStream_t>(main_stream),
+                                  static_cast<cudaStream_t>(side_stream));
 }
 
 int tbik_ar_trace(tbik_ar_t comm, uint64_t* out, int max_blocks, int* blocks) {

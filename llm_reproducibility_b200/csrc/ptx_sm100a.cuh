@@ -34,17 +34,6 @@ TBIK_DEVICE bool elect_one() {
 }
 
 
-// Re-balance the register file between warpgroups (4 consecutive warps): the producer / issuer
-// warps give registers back, the epilogue warps take them.  Counts are per thread, multiples of 8.
-template <int N>
-TBIK_DEVICE void setmaxnreg_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N>
-TBIK_DEVICE void setmaxnreg_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
-
 // ---------------------------------------------------------------- mbarrier
 TBIK_DEVICE void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));

@@ -17,6 +17,7 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
                 int dtype, int leaf, int node_dtype, int max_ctas, int tiling, void* workspace, size_t ws_bytes,
                 cudaStream_t stream, int splits);  // splits: 0 = automatic (tiling 0 only), 1 = none, 2..16 = K-slabs
 size_t gemm_workspace_bytes(int M, int N, int64_t K, int leaf);
+int gemm_plan_query(int M, int N, int64_t K, int leaf, int max_ctas, size_t ws_bytes, int out[4]);
 size_t gemm_split_workspace_bytes(int M, int N, int64_t K, int leaf, int tiling, int splits);
 size_t gemm_static_scratch_bytes();
 int gemm_static_accepts(int M, int N, int64_t K, int leaf);
@@ -36,6 +37,10 @@ int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, vo
            bool tree, cudaStream_t stream);
 int ar_run_within(tbik_ar_t h, const void* reg_base, size_t byte_offset, void* out, int64_t numel, int dtype,
                   cudaStream_t stream);
+int ar_row_split_layer(tbik_ar_t h, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
+                       int64_t ldw, int dtype, int leaf, void* reg_base, size_t reg_bytes, void* workspace,
+                       size_t ws_bytes, const int* block_rows, int nblk, int comm_ctas, cudaStream_t main,
+                       cudaStream_t side);
 int ar_trace(tbik_ar_t h, uint64_t* out, int max_blocks, int* blocks);
 int ar_graph_meta_count(tbik_ar_t h, int* n);
 int ar_graph_meta(tbik_ar_t h, void* handles_out, int64_t* offsets_out);

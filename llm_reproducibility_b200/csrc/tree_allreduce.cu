@@ -120,6 +120,8 @@ struct ArArgs {
   uint64_t* trace;  // optional (host-mapped): [block][8] globaltimer stamps of the phases of the last launch
   int rank;
   int chunks;       // push schedule only
+  int keep_input;   // one-shot: 1 = the caller promises not to overwrite the input before the NEXT collective of
+                    // this communicator has passed its first barrier, so the closing barrier is left out
 };
 
 __device__ __forceinline__ void stamp(const ArArgs& a, int slot) {
@@ -164,8 +166,9 @@ __global__ void __launch_bounds__(kThreads, 1) allreduce_oneshot_kernel(const Ar
   reduce_range<T, NG, TREE, VEC, UNROLL>(dp, a.in_off, 0, a.nvec, tid, stride,
                                          [&](int64_t i, const Vec<VEC>& v) { st_vec<VEC>(out, i, v); });
   stamp(a, 2);
-  // peers may still be reading this rank's buffer: nobody leaves before everybody is done
-  block_barrier<NG>(a.sg, a.self, a.rank, a.status, a.limit_ns, 3, &fail);
+  // peers may still be reading this rank's buffer: nobody leaves before everybody is done -- unless the caller
+  // keeps the buffer untouched until a later collective's first barrier has said the same thing
+  if (a.keep_input == 0) block_barrier<NG>(a.sg, a.self, a.rank, a.status, a.limit_ns, 3, &fail);
   stamp(a, 4);
 }
 
@@ -344,6 +347,8 @@ struct Communicator {
   bool poisoned = false;
   int vec_packs = 0;             // 0 / 1 = 128-bit accesses, 2 = 256-bit
   int loads_in_flight = 0;       // 0 = built-in policy
+  int cluster_pairs = 1;         // launch CTAs as clusters of two (placement only)
+  std::vector<cudaEvent_t> events;  // hand-overs between the two streams of the row-block pipeline
   uint64_t* trace_host = nullptr;  // phase stamps of the last launch (host-mapped), when tracing is on
   uint64_t* trace_dev = nullptr;
   int trace_blocks = 0;
@@ -353,16 +358,32 @@ static Communicator* as_comm(tbik_ar_t h) { return reinterpret_cast<Communicator
 
 enum Schedule { kOneShot = 0, kTwoShot = 1, kPush = 2 };
 
+// `pairs`: launch the CTAs as clusters of two.  The kernels use no cluster feature; the point is placement: a
+// cluster occupies both SMs of a pair, so an all-reduce that runs beside a GEMM whose CTAs are themselves pairs
+// takes whole pairs away from it instead of halves of many.
 template <typename T, int NG, bool TREE, int VEC, int UNROLL>
-static int launch_kernel(const ArArgs& a, int sched, int blocks, int threads, cudaStream_t stream) {
+static int launch_kernel(const ArArgs& a, int sched, int blocks, int threads, cudaStream_t stream, bool pairs) {
+  void (*kernel)(const ArArgs) = allreduce_oneshot_kernel<T, NG, TREE, VEC, UNROLL>;
   if (sched == kPush) {
-    if constexpr (NG >= 2) allreduce_push_kernel<T, NG, TREE, VEC, UNROLL><<<blocks, threads, 0, stream>>>(a);
+    if constexpr (NG >= 2) kernel = allreduce_push_kernel<T, NG, TREE, VEC, UNROLL>;
   } else if (sched == kTwoShot) {
-    allreduce_twoshot_kernel<T, NG, TREE, VEC, UNROLL><<<blocks, threads, 0, stream>>>(a);
-  } else {
-    allreduce_oneshot_kernel<T, NG, TREE, VEC, UNROLL><<<blocks, threads, 0, stream>>>(a);
+    kernel = allreduce_twoshot_kernel<T, NG, TREE, VEC, UNROLL>;
   }
-  cudaError_t e = cudaGetLastError();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
+  cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  if (pairs && blocks % 2 == 0) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, a);
   if (e != cudaSuccess) return set_cuda_error(e, "all-reduce kernel launch");
   return TBIK_OK;
 }
@@ -371,7 +392,8 @@ static int launch_kernel(const ArArgs& a, int sched, int blocks, int threads, cu
 // built-in 16 for 4 and 8 ranks, 8 for 2).  The tuned variants exist for the path the row-split layer uses (bf16,
 // tree order); everything else runs the built-in shape.
 template <typename T, int NG, bool TREE>
-static int launch_ar(const ArArgs& a, int sched, int blocks, int threads, cudaStream_t stream, int vec, int loads) {
+static int launch_ar(const ArArgs& a, int sched, int blocks, int threads, cudaStream_t stream, int vec, int loads,
+                     bool pairs) {
   constexpr int kDefaultUnroll = NG >= 6 ? 2 : 4;
   if constexpr (std::is_same<T, __nv_bfloat16>::value && TREE && NG >= 2) {
     int unroll = loads > 0 ? loads / (NG * vec) : kDefaultUnroll / vec;
@@ -379,47 +401,47 @@ static int launch_ar(const ArArgs& a, int sched, int blocks, int threads, cudaSt
     while (unroll * NG * vec > 32) unroll /= 2;  // at most 32 packs = 128 registers of payload per thread
     if (vec == 2) {
       switch (unroll) {
-        case 1: return launch_kernel<T, NG, TREE, 2, 1>(a, sched, blocks, threads, stream);
-        case 2: return launch_kernel<T, NG, TREE, 2, 2>(a, sched, blocks, threads, stream);
+        case 1: return launch_kernel<T, NG, TREE, 2, 1>(a, sched, blocks, threads, stream, pairs);
+        case 2: return launch_kernel<T, NG, TREE, 2, 2>(a, sched, blocks, threads, stream, pairs);
         case 4:
-          if constexpr (NG <= 4) return launch_kernel<T, NG, TREE, 2, 4>(a, sched, blocks, threads, stream);
+          if constexpr (NG <= 4) return launch_kernel<T, NG, TREE, 2, 4>(a, sched, blocks, threads, stream, pairs);
           break;
         case 8:
-          if constexpr (NG <= 2) return launch_kernel<T, NG, TREE, 2, 8>(a, sched, blocks, threads, stream);
+          if constexpr (NG <= 2) return launch_kernel<T, NG, TREE, 2, 8>(a, sched, blocks, threads, stream, pairs);
           break;
         default: break;
       }
-      return launch_kernel<T, NG, TREE, 2, 1>(a, sched, blocks, threads, stream);
+      return launch_kernel<T, NG, TREE, 2, 1>(a, sched, blocks, threads, stream, pairs);
     }
     switch (unroll) {
-      case 1: return launch_kernel<T, NG, TREE, 1, 1>(a, sched, blocks, threads, stream);
-      case 2: return launch_kernel<T, NG, TREE, 1, 2>(a, sched, blocks, threads, stream);
-      case 4: return launch_kernel<T, NG, TREE, 1, 4>(a, sched, blocks, threads, stream);
+      case 1: return launch_kernel<T, NG, TREE, 1, 1>(a, sched, blocks, threads, stream, pairs);
+      case 2: return launch_kernel<T, NG, TREE, 1, 2>(a, sched, blocks, threads, stream, pairs);
+      case 4: return launch_kernel<T, NG, TREE, 1, 4>(a, sched, blocks, threads, stream, pairs);
       case 8:
-        if constexpr (NG <= 4) return launch_kernel<T, NG, TREE, 1, 8>(a, sched, blocks, threads, stream);
+        if constexpr (NG <= 4) return launch_kernel<T, NG, TREE, 1, 8>(a, sched, blocks, threads, stream, pairs);
         break;
       case 16:
-        if constexpr (NG <= 2) return launch_kernel<T, NG, TREE, 1, 16>(a, sched, blocks, threads, stream);
+        if constexpr (NG <= 2) return launch_kernel<T, NG, TREE, 1, 16>(a, sched, blocks, threads, stream, pairs);
         break;
       default: break;
     }
   }
-  return launch_kernel<T, NG, TREE, 1, kDefaultUnroll>(a, sched, blocks, threads, stream);
+  return launch_kernel<T, NG, TREE, 1, kDefaultUnroll>(a, sched, blocks, threads, stream, pairs);
 }
 
 template <typename T, bool TREE>
 static int dispatch_world(int world, const ArArgs& a, int sched, int blocks, int threads, cudaStream_t stream, int vec,
-                          int loads) {
+                          int loads, bool pairs) {
   switch (world) {
     case 1:
-      if constexpr (TREE) return launch_ar<T, 1, TREE>(a, kOneShot, blocks, threads, stream, 1, 0);
+      if constexpr (TREE) return launch_ar<T, 1, TREE>(a, kOneShot, blocks, threads, stream, 1, 0, pairs);
       break;
-    case 2: return launch_ar<T, 2, TREE>(a, sched, blocks, threads, stream, vec, loads);
-    case 4: return launch_ar<T, 4, TREE>(a, sched, blocks, threads, stream, vec, loads);
+    case 2: return launch_ar<T, 2, TREE>(a, sched, blocks, threads, stream, vec, loads, pairs);
+    case 4: return launch_ar<T, 4, TREE>(a, sched, blocks, threads, stream, vec, loads, pairs);
     case 6:
-      if constexpr (!TREE) return launch_ar<T, 6, TREE>(a, sched, blocks, threads, stream, vec, loads);
+      if constexpr (!TREE) return launch_ar<T, 6, TREE>(a, sched, blocks, threads, stream, vec, loads, pairs);
       break;
-    case 8: return launch_ar<T, 8, TREE>(a, sched, blocks, threads, stream, vec, loads);
+    case 8: return launch_ar<T, 8, TREE>(a, sched, blocks, threads, stream, vec, loads, pairs);
     default: break;
   }
   return set_error(TBIK_ERR_SHAPE, TREE ? "tree all-reduce supports 1, 2, 4 or 8 ranks"
@@ -430,7 +452,8 @@ static int dispatch_world(int world, const ArArgs& a, int sched, int blocks, int
 // registered buffer that starts at reg_base (a producer wrote it in place); else it must itself be registered
 // (or the stream is capturing).
 static int ar_run_impl(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, void* reg_buffer,
-                       size_t reg_bytes, const void* reg_base, bool tree, cudaStream_t stream) {
+                       size_t reg_bytes, const void* reg_base, bool tree, cudaStream_t stream, int max_blocks = -1,
+                       bool keep_input = false) {
   Communicator* c = as_comm(h);
   if (!c) return set_error(TBIK_ERR_ARG, "all-reduce: null communicator");
   if (c->status_host && c->status_host->w[0] != 0) c->poisoned = true;
@@ -507,13 +530,14 @@ static int ar_run_impl(tbik_ar_t h, const void* inp, void* out, int64_t numel, i
     }
   }
   // 256-bit accesses when asked for and every address involved is 32-byte aligned
-  int vec = c->vec_packs == 2 ? 2 : 1;
+  int vec = (c->vec_packs == 2 && dtype == TBIK_DTYPE_BF16 && tree && c->world >= 2) ? 2 : 1;
   if (vec == 2 && (npacks % 2 != 0 || byte_off % 32 != 0 || (reinterpret_cast<uintptr_t>(out) & 31u) != 0 ||
                    (reinterpret_cast<uintptr_t>(src) & 31u) != 0))
     vec = 1;
   const int64_t nvec = npacks / vec;
   const int64_t work = twoshot ? (nvec + c->world - 1) / c->world : nvec;
-  int cap_blocks = c->max_blocks > 0 ? c->max_blocks : (bytes <= (256u << 10) ? 36 : c->sm_count);
+  const int want_blocks = max_blocks >= 0 ? max_blocks : c->max_blocks;
+  int cap_blocks = want_blocks > 0 ? want_blocks : (bytes <= (256u << 10) ? 36 : c->sm_count);
   if (cap_blocks > kMaxBlocks) cap_blocks = kMaxBlocks;
   const int threads = c->threads > 0 ? c->threads : kThreads;
   // every block of a launch must be resident at once (block b waits for block b of the peers)
@@ -535,17 +559,19 @@ static int ar_run_impl(tbik_ar_t h, const void* inp, void* out, int64_t numel, i
   a.trace = c->trace_dev;
   a.rank = c->rank;
   a.chunks = push_chunks;
+  a.keep_input = keep_input ? 1 : 0;
   if (c->trace_host) c->trace_blocks = blocks;
   const int sched = push_chunks > 0 ? kPush : (twoshot ? kTwoShot : kOneShot);
   const int loads = c->loads_in_flight;
+  const bool pairs = c->cluster_pairs != 0 && blocks % 2 == 0;
   if (dtype == TBIK_DTYPE_FP32)
-    return tree ? dispatch_world<float, true>(c->world, a, sched, blocks, threads, stream, vec, loads)
-                : dispatch_world<float, false>(c->world, a, sched, blocks, threads, stream, vec, loads);
+    return tree ? dispatch_world<float, true>(c->world, a, sched, blocks, threads, stream, vec, loads, pairs)
+                : dispatch_world<float, false>(c->world, a, sched, blocks, threads, stream, vec, loads, pairs);
   if (dtype == TBIK_DTYPE_FP16)
-    return tree ? dispatch_world<__half, true>(c->world, a, sched, blocks, threads, stream, vec, loads)
-                : dispatch_world<__half, false>(c->world, a, sched, blocks, threads, stream, vec, loads);
-  return tree ? dispatch_world<__nv_bfloat16, true>(c->world, a, sched, blocks, threads, stream, vec, loads)
-              : dispatch_world<__nv_bfloat16, false>(c->world, a, sched, blocks, threads, stream, vec, loads);
+    return tree ? dispatch_world<__half, true>(c->world, a, sched, blocks, threads, stream, vec, loads, pairs)
+                : dispatch_world<__half, false>(c->world, a, sched, blocks, threads, stream, vec, loads, pairs);
+  return tree ? dispatch_world<__nv_bfloat16, true>(c->world, a, sched, blocks, threads, stream, vec, loads, pairs)
+              : dispatch_world<__nv_bfloat16, false>(c->world, a, sched, blocks, threads, stream, vec, loads, pairs);
 }
 
 int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, void* reg_buffer, size_t reg_bytes,
@@ -558,6 +584,68 @@ int ar_run_within(tbik_ar_t h, const void* reg_base, size_t byte_offset, void* o
   if (!reg_base) return set_error(TBIK_ERR_ARG, "all-reduce: null registered buffer");
   return ar_run_impl(h, static_cast<const char*>(reg_base) + byte_offset, out, numel, dtype, nullptr, 0, reg_base, true,
                      stream);
+}
+
+// Row-split layer as a pipeline over blocks of rows: the GEMM of block i + 1 runs on `main` while the tree
+// all-reduce of block i runs on `side` with a few CTAs.  Everything is enqueued from here in one go (launches,
+// event records and waits), so the host spends microseconds per block, not tens of them.
+int ar_row_split_layer(tbik_ar_t h, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
+                       int64_t ldw, int dtype, int leaf, void* reg_base, size_t reg_bytes, void* workspace,
+                       size_t ws_bytes, const int* block_rows, int nblk, int comm_ctas, cudaStream_t main,
+                       cudaStream_t side) {
+  Communicator* c = as_comm(h);
+  if (!c) return set_error(TBIK_ERR_ARG, "row-split layer: null communicator");
+  if (dtype != TBIK_DTYPE_BF16 && dtype != TBIK_DTYPE_FP16) return set_error(TBIK_ERR_DTYPE, "row-split layer: bf16 or fp16");
+  if (M <= 0 || N <= 0 || K <= 0 || !A || !W || !out || !reg_base) return set_error(TBIK_ERR_ARG, "row-split layer: bad argument");
+  if (static_cast<size_t>(M) * N * 2 > reg_bytes) return set_error(TBIK_ERR_SHAPE, "row-split layer: result larger than the registered buffer");
+  if (N % 8 != 0) return set_error(TBIK_ERR_SHAPE, "row-split layer: N must be a multiple of 8");
+  if (!block_rows || nblk < 1 || nblk > 64) return set_error(TBIK_ERR_ARG, "row-split layer: 1 to 64 blocks of rows");
+  {
+    int64_t total = 0;
+    for (int b = 0; b < nblk; ++b) {
+      if (block_rows[b] <= 0) return set_error(TBIK_ERR_SHAPE, "row-split layer: every block needs at least one row");
+      total += block_rows[b];
+    }
+    if (total != M) return set_error(TBIK_ERR_SHAPE, "row-split layer: the blocks must add up to M rows");
+  }
+  if (main == side) return set_error(TBIK_ERR_ARG, "row-split layer: the two streams must differ");
+  while (static_cast<int>(c->events.size()) < nblk + 1) {
+    cudaEvent_t ev;
+    cudaError_t e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+    if (e != cudaSuccess) return set_cuda_error(e, "cudaEventCreateWithFlags");
+    c->events.push_back(ev);
+  }
+  if (comm_ctas < 2 || comm_ctas > c->sm_count / 2) return set_error(TBIK_ERR_ARG, "row-split layer: comm_ctas out of range");
+  // (letting both kernels have every SM, the all-reduce as small CTAs beside the resident GEMM CTAs, was measured
+  // too: it slows the GEMM more than the SMs given away here)
+  const int gemm_ctas = c->sm_count - comm_ctas;
+  const char* a = static_cast<const char*>(A);
+  char* part = static_cast<char*>(reg_base);
+  char* o = static_cast<char*>(out);
+  int r0 = 0;
+  for (int b = 0; b < nblk; r0 += block_rows[b], ++b) {
+    const int rows = block_rows[b];
+    const size_t off = static_cast<size_t>(r0) * N * 2;
+    // the first block has the GPU to itself; the later ones leave SMs to the all-reduce of their predecessor
+    int rc = gemm_launch(a + static_cast<size_t>(r0) * lda * 2, W, part + off, rows, N, K, lda, ldw, N, dtype, leaf,
+                         TBIK_NODE_INPUT, b == 0 ? 0 : gemm_ctas, 0, workspace, ws_bytes, main, 0);
+    if (rc != TBIK_OK) return rc;
+    cudaError_t e = cudaEventRecord(c->events[b], main);
+    if (e != cudaSuccess) return set_cuda_error(e, "cudaEventRecord");
+    e = cudaStreamWaitEvent(side, c->events[b], 0);
+    if (e != cudaSuccess) return set_cuda_error(e, "cudaStreamWaitEvent");
+    const bool last = b == nblk - 1;
+    // Only the layer's last all-reduce closes with a barrier: the blocks before it occupy other rows of the
+    // registered buffer, which nobody writes again before that barrier has been passed.
+    rc = ar_run_impl(h, part + off, o + off, static_cast<int64_t>(rows) * N, dtype, nullptr, 0, reg_base, true, side,
+                     last ? 0 : comm_ctas, !last);
+    if (rc != TBIK_OK) return rc;
+  }
+  cudaError_t e = cudaEventRecord(c->events[nblk], side);
+  if (e != cudaSuccess) return set_cuda_error(e, "cudaEventRecord");
+  e = cudaStreamWaitEvent(main, c->events[nblk], 0);
+  if (e != cudaSuccess) return set_cuda_error(e, "cudaStreamWaitEvent");
+  return TBIK_OK;
 }
 
 size_t ar_meta_size() { return sizeof(Signal); }
@@ -605,6 +693,7 @@ int ar_destroy(tbik_ar_t h) {
   for (auto& kv : c->opened) cudaIpcCloseMemHandle(kv.second);
   if (c->status_host) cudaFreeHost(c->status_host);
   if (c->trace_host) cudaFreeHost(c->trace_host);
+  for (cudaEvent_t ev : c->events) cudaEventDestroy(ev);
   delete c;
   return TBIK_OK;
 }
@@ -630,6 +719,7 @@ int ar_configure(tbik_ar_t h, int key, int64_t value) {
       if (value < 0 || value > 32) return set_error(TBIK_ERR_ARG, "tbik_ar_configure: loads in flight must be 0..32");
       c->loads_in_flight = static_cast<int>(value);
       return TBIK_OK;
+    case TBIK_AR_CFG_CLUSTER_PAIRS: c->cluster_pairs = value != 0 ? 1 : 0; return TBIK_OK;
     case TBIK_AR_CFG_TRACE:
       if (value != 0 && c->trace_host == nullptr) {
         cudaError_t e = cudaHostAlloc(reinterpret_cast<void**>(&c->trace_host), sizeof(uint64_t) * 8 * kMaxBlocks, cudaHostAllocMapped);

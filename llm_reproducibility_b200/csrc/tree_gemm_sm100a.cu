@@ -75,6 +75,10 @@ struct GemmParams {
   int64_t ldo;
   int n_out;             // true number of columns (N above is rounded up to 8 for the roots)
   uint32_t* counters;    // arrivals per 128-row block of an output tile; zero before and after every launch
+  // Bytes one TMA load of A delivers per stage.  With fewer than 128 rows of A the box covers only 16, 32 or 64
+  // rows: the rest of the 128-row shared-memory tile keeps whatever it held, the UMMA multiplies that too, and
+  // the rows of C it produces are never stored (a row of C depends on no other row of A).
+  uint32_t a_box_bytes;
   uint32_t* status;      // [0] error code, [1] block, [2] role, [3] SM cycles of block 0 (last launch)
 };
 
@@ -246,7 +250,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           // every CTA tracks its own bytes on its own barrier
-          mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
+          mbar_arrive_expect_tx(full_bar(stage), p.a_box_bytes + C_::B_STAGE_BYTES);
           tma_load_2d(sa, &tmap_a, (kb0 + kb) * BK, row0, full_bar(stage));
           tma_load_2d(sa + A_STAGE_BYTES, &tmap_b, (kb0 + kb) * BK, wrow0, full_bar(stage));
           if (++stage == STAGES) {
@@ -814,8 +818,11 @@ int sm_count(int dev) {
   if (dev < 0 || dev >= kMaxDevices) dev = 0;
   int n = cached[dev].load(std::memory_order_relaxed);
   if (n == 0) {
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 1;
+    // without a device (plan queries on a build machine) answer for the GPU this library is written for
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = 148;
+    }
     cached[dev].store(n, std::memory_order_relaxed);
   }
   return n;
@@ -901,28 +908,36 @@ static Plan make_plan(int tiling, int M, int N, int L, int max_ctas, int splits 
   return pl;
 }
 
-// Rough time of a plan in microseconds, fitted to measurements at 16..512 rows of C (N = 4096, K = 1536..12288):
-// a CTA advances one 64-wide k-block every 0.155 us (32-column tile) .. 0.53 us (256 columns), launch and
-// prologue cost 3.5 us; with K-slabs the last CTA of every tile re-reads the slab roots (from L2) and adds them.
+// Rough time of a plan in microseconds, fitted to measurements under a CUDA graph with the weight streaming from
+// HBM (N = 4096, K = 4096 and 12288, 1..256 rows of C, every tiling x 1..16 slabs): launch, prologue and pipeline
+// fill cost 4 us; a CTA advances one 64-wide k-block every 0.155 us (32-column tile) .. 0.53 us (256 columns);
+// all CTAs together cannot stream the operands faster than HBM delivers them (5.8 TB/s in this access pattern);
+// with K-slabs the arrival protocol and the last CTA's pass over the roots add 2 - 5 us depending on the tiling.
 static double plan_cost_us(const Plan& pl, int M, int N, int kblocks_total, int ctas) {
   const Variant& v = kVariants[pl.tiling - 1][pl.deep ? 1 : 0];
   const int items = pl.tiles_m * pl.tiles_n * pl.splits;
   const int units = v.pair ? ctas / 2 : ctas;
   const int waves = (items + units - 1) / (units > 0 ? units : 1);
-  const double per_kblock = v.bn >= 256 ? 0.53 : v.bn == 128 ? (v.pair ? 0.18 : 0.23) : v.bn == 64 ? 0.17 : 0.155;
-  double t = 3.5 + waves * (kblocks_total / pl.splits) * per_kblock;
-  if (pl.splits > 1) t += 0.8 + 0.12 * pl.splits + static_cast<double>(pl.splits + 1) * M * N * 2 / 3.0e6;
+  static const double per_kblock[6] = {0.223, 0.19, 0.53, 0.44, 0.171, 0.155};
+  static const double slab_overhead[6] = {5.0, 5.0, 2.3, 4.0, 2.2, 5.0};
+  const double stream_bytes = (static_cast<double>(N) + M) * kblocks_total * BK * 2;
+  double stream = waves * static_cast<double>(kblocks_total / pl.splits) * per_kblock[pl.tiling - 1];
+  if (stream < stream_bytes / 5.8e6) stream = stream_bytes / 5.8e6;
+  double t = 4.0 + stream;
+  if (pl.splits > 1)
+    t += slab_overhead[pl.tiling - 1] + 0.3 * (log2_int(pl.splits) - 1) + static_cast<double>(pl.splits + 1) * M * N * 2 / 3.0e6;
   return t;
 }
 
 // Automatic choice: the first tiling, in order of measured speed at large M (256x128 per CTA pair: operands
 // shared by two SMs, the whole tree stack in tensor memory, eight pipeline stages; then 128x256, 128x128),
-// that still gives (nearly) every SM a tile; with few rows of C the GEMM streams W from HBM and needs all SMs
-// pulling, so the narrow tilings follow.  128x256 needs the caller's scratch for the upper tree levels.
+// that still gives (nearly) every SM a tile.  128x256 needs the caller's scratch for the upper tree levels.
 //
-// When even the narrowest tiling leaves SMs idle (decode-sized M), K is cut into slabs as well: every candidate
-// (tiling, slabs) that fits one wave and the caller's workspace is costed and the cheapest wins.  `groups` is the
-// number of level-0 groups of the tree (T / F), the finest cut that keeps every slab a whole subtree.
+// With fewer rows of C than that (decode-sized M) the GEMM streams W from HBM and needs every SM pulling: every
+// (tiling, slabs) combination that fits the caller's workspace is costed -- K cut into 1, 2, 4, 8 or 16 slabs, at
+// most one wave of work items when K is cut -- and the cheapest wins.  `groups` is the number of level-0 groups of
+// the tree (T / F), the finest cut that keeps every slab a whole subtree.  The choice is a function of the sizes
+// only, and no choice changes a bit of the result.
 static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int max_ctas, size_t ws_bytes, bool have_ws) {
   int ctas = sm_count(current_device());
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
@@ -933,40 +948,31 @@ static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int ma
   const bool short_k = kblocks_total <= 24;
   const int order[6] = {short_k ? 4 : 2, short_k ? 2 : 4, 3, 1, 5, 6};
   constexpr int kOrder = 6;
-  Plan best{};
-  bool have = false;
-  for (int i = 0; i < kOrder; ++i) {
+  for (int i = 0; i < 4; ++i) {
     if (!short_k && order[i] == 4) continue;  // long K: 256x256 only adds scratch need
     Plan pl = make_plan(order[i], M, N, L, max_ctas);
     if (pl.scratch_bytes > 0 && !(have_ws && pl.scratch_bytes <= ws_bytes)) continue;
     const Variant& pv = kVariants[order[i] - 1][pl.deep ? 1 : 0];
-    if (pl.tiles_m * pl.tiles_n * (pv.pair ? 2 : 1) >= enough) {
-      if (order[i] <= 4 || !have_ws || groups < 2) return pl;  // enough rows of C: no slabs
-      best = pl;
-      have = true;
-      break;
-    }
-    if (!have || pl.tiles_m * pl.tiles_n > best.tiles_m * best.tiles_n) {
-      best = pl;
-      have = true;
-    }
+    if (pl.tiles_m * pl.tiles_n * (pv.pair ? 2 : 1) >= enough) return pl;  // enough rows of C
   }
-  if (!have) best = make_plan(1, M, N, L, max_ctas);
-  if (!have_ws || groups < 2) return best;
-  double best_cost = plan_cost_us(best, M, N, kblocks_total, ctas);
+  Plan best{};
+  double best_cost = 0.0;
+  bool have = false;
   for (int i = 0; i < kOrder; ++i) {
-    if (order[i] == 4) continue;
-    for (int s = 2; s <= kMaxSplits && s <= groups; s *= 2) {
+    for (int s = 1; s <= kMaxSplits; s *= 2) {
+      if (s > 1 && (!have_ws || s > groups)) break;
       Plan pl = make_plan(order[i], M, N, L, max_ctas, s);
-      if (pl.tiles_m * pl.tiles_n * s * (kVariants[order[i] - 1][0].pair ? 2 : 1) > ctas) break;  // one wave only
-      if (!pl.valid || pl.total_bytes() > ws_bytes) continue;
+      if (s > 1 && pl.tiles_m * pl.tiles_n * s * (kVariants[order[i] - 1][0].pair ? 2 : 1) > ctas) break;  // one wave only
+      if (!pl.valid || (pl.total_bytes() > 0 && !(have_ws && pl.total_bytes() <= ws_bytes))) continue;
       const double c = plan_cost_us(pl, M, N, kblocks_total, ctas);
-      if (c < best_cost) {
+      if (!have || c < best_cost) {
         best = pl;
         best_cost = c;
+        have = true;
       }
     }
   }
+  if (!have) best = make_plan(1, M, N, L, max_ctas);
   return best;
 }
 
@@ -975,6 +981,17 @@ size_t gemm_workspace_bytes(int M, int N, int64_t K, int leaf) {
   if (M <= 0 || N <= 0 || tree_shape(K, leaf, &T, &F, &L) != TBIK_OK) return 0;
   // what the automatic choice would like to have if scratch were unlimited
   return auto_plan(M, N, L, T / F, T * (leaf / BK), 0, ~size_t(0), true).total_bytes();
+}
+
+int gemm_plan_query(int M, int N, int64_t K, int leaf, int max_ctas, size_t ws_bytes, int out[4]) {
+  int T, F, L;
+  if (M <= 0 || N <= 0 || tree_shape(K, leaf, &T, &F, &L) != TBIK_OK) return set_error(TBIK_ERR_SHAPE, "tbik_gemm_plan: bad sizes");
+  const Plan pl = auto_plan(M, N, L, T / F, T * (leaf / BK), max_ctas, ws_bytes, ws_bytes > 0);
+  out[0] = pl.tiling;
+  out[1] = pl.splits;
+  out[2] = pl.grid;
+  out[3] = pl.deep ? 1 : 0;
+  return TBIK_OK;
 }
 
 size_t gemm_split_workspace_bytes(int M, int N, int64_t K, int leaf, int tiling, int splits) {
@@ -992,13 +1009,17 @@ static int gemm_launch_plan(const void* A, const void* W, void* C, int M, int N,
   const Variant& v = kVariants[pl.tiling - 1][pl.deep ? 1 : 0];
   const int dev = current_device();
 
+  // rows of A per TMA box: all 128 of a CTA's tile, or just enough for a decode-sized M (16, 32, 64)
+  int a_box = BM;
+  if (!v.pair && M <= 64) a_box = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   CUtensorMap ta, tb;
-  int rc = make_tmap(&ta, dtype, A, M, K, lda, BM);
+  int rc = make_tmap(&ta, dtype, A, M, K, lda, a_box);
   if (rc != TBIK_OK) return rc;
   rc = make_tmap(&tb, dtype, W, N, K, ldw, v.pair ? v.bn / 2 : v.bn);
   if (rc != TBIK_OK) return rc;
 
   GemmParams p{};
+  p.a_box_bytes = static_cast<uint32_t>(a_box) * BK * 2;
   p.C = C;
   p.ldc = ldc;
   p.M = M;

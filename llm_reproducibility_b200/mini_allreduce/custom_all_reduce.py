@@ -116,7 +116,8 @@ class CustomAllreduce:
         if self._max_blocks_default > 0:
             ops.configure(self._ptr, ops.CFG_MAX_BLOCKS, self._max_blocks_default)
         for env, key in (("TBIK_AR_VEC_PACKS", ops.CFG_VEC_PACKS), ("TBIK_AR_LOADS_IN_FLIGHT", ops.CFG_LOADS_IN_FLIGHT),
-                         ("TBIK_AR_THREADS", ops.CFG_THREADS), ("TBIK_AR_ONESHOT_MAX_BYTES", ops.CFG_ONESHOT_MAX_BYTES)):
+                         ("TBIK_AR_THREADS", ops.CFG_THREADS), ("TBIK_AR_ONESHOT_MAX_BYTES", ops.CFG_ONESHOT_MAX_BYTES),
+                         ("TBIK_AR_CLUSTER_PAIRS", ops.CFG_CLUSTER_PAIRS)):
             if os.environ.get(env):
                 ops.configure(self._ptr, key, int(os.environ[env]))
         ops.register_buffer(self._ptr, self.buffer_ptrs)
@@ -199,19 +200,6 @@ class CustomAllreduce:
         else:
             self._native_all_reduce(self._ptr, inp, out, self.buffer_ptrs[self.rank], self.max_size)
         return out
-
-    def tree_all_reduce_rows(self, view: torch.Tensor, out: torch.Tensor, max_blocks: int = 0) -> None:
-        """Tree all-reduce of `view`, a slice of `registered_view(...)` that a producer filled in place, into
-        `out`, on the current stream; `max_blocks` > 0 bounds the CTAs of this launch (the row-split layer
-        reduces one block of rows with a few CTAs while the GEMM computes the next block on the others)."""
-        base = self.buffer_ptrs[self.rank]
-        offset = view.data_ptr() - base
-        assert 0 <= offset and offset + view.numel() * view.element_size() <= self.max_size
-        ops.configure(self._ptr, ops.CFG_MAX_BLOCKS, max_blocks)
-        try:
-            ops.tree_all_reduce_within(self._ptr, base, offset, out)
-        finally:
-            ops.configure(self._ptr, ops.CFG_MAX_BLOCKS, self._max_blocks_default)
 
     def registered_view(self, shape, dtype: torch.dtype) -> Optional[torch.Tensor]:
         """A tensor that aliases the start of this rank's IPC-registered data buffer, or None if it

@@ -60,6 +60,12 @@ def tree_all_reduce_within(fa: int, reg_base: int, byte_offset: int, out: torch.
     _custom_ar.tree_all_reduce_within(fa, reg_base, byte_offset, out)
 
 
+def row_split_layer(fa: int, A: torch.Tensor, B: torch.Tensor, reg_base: int, reg_bytes: int, block_rows: List[int],
+                    comm_ctas: int, side_stream: int, leaf: int = 0) -> torch.Tensor:
+    """Row-split GEMM + tree all-reduce pipelined over blocks of rows on two streams (addition)."""
+    return _custom_ar.row_split_layer(fa, A, B, reg_base, reg_bytes, block_rows, comm_ctas, side_stream, leaf)
+
+
 def trace(fa: int) -> List[int]:
     """Per-CTA phase time stamps of the last launch; needs configure(CFG_TRACE, 1) (addition)."""
     return _custom_ar.trace(fa)
@@ -67,7 +73,7 @@ def trace(fa: int) -> List[int]:
 
 # keys of `configure`
 CFG_SCRATCH_BYTES, CFG_ONESHOT_MAX_BYTES, CFG_MAX_BLOCKS, CFG_WAIT_LIMIT_NS, CFG_THREADS = 1, 2, 3, 4, 5
-CFG_PUSH_MIN_BYTES, CFG_PUSH_CHUNKS, CFG_VEC_PACKS, CFG_LOADS_IN_FLIGHT, CFG_TRACE = 6, 7, 8, 9, 10
+CFG_PUSH_MIN_BYTES, CFG_PUSH_CHUNKS, CFG_VEC_PACKS, CFG_LOADS_IN_FLIGHT, CFG_TRACE, CFG_CLUSTER_PAIRS = 6, 7, 8, 9, 10, 11
 
 
 def configure(fa: int, key: int, value: int) -> None:

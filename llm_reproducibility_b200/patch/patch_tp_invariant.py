@@ -11,7 +11,25 @@ from typing import Callable, Optional
 import torch
 
 from ..tbik.tree_based_all_reduce import tree_matmul_all_reduce
-from ..tbik.tree_based_matmul import matmul_tp_persistent
+from ..tbik.tree_based_matmul import leaf_for, matmul_tp_persistent
+
+# Largest tensor-parallel degree whose results must agree bit for bit with every smaller one (TP = 1 included).
+# It fixes the leaf width of every row-split layer from the layer's FULL K, so that engines started with
+# different TP degrees walk the same reduction tree.  Set through `patch_tp_invariant(max_tp=...)`.
+MAX_TP = 8
+
+
+def layer_leaf(K_total: int, tp_size: int, dtype: torch.dtype) -> int:
+    """Leaf width of a layer with unsharded reduction length K_total: sized for MAX_TP ranks; a layer too short
+    for that many aligned subtrees is sized for the largest degree below it that still covers `tp_size`."""
+    max_tp = max(MAX_TP, tp_size)
+    while True:
+        try:
+            return leaf_for(K_total, max_tp, dtype)
+        except ValueError:
+            if max_tp // 2 < max(tp_size, 1):
+                raise
+            max_tp //= 2
 
 
 def row_parallel_forward(self, input_, *, device_group_fn: Optional[Callable] = None,
@@ -34,11 +52,13 @@ def row_parallel_forward(self, input_, *, device_group_fn: Optional[Callable] = 
     # the bias is added once, after the reduction, and only where it is not skipped
     lead = input_parallel.shape[:-1]
     x2d = input_parallel.reshape(-1, input_parallel.shape[-1])
+    # one leaf width per layer, derived from the unsharded K: the same at every TP degree
+    leaf = layer_leaf(x2d.shape[-1] * self.tp_size, self.tp_size, x2d.dtype)
     if self.reduce_results and self.tp_size > 1:
         group = device_group_fn() if device_group_fn is not None else None
-        output = tree_matmul_all_reduce(x2d, self.weight.t(), group)
+        output = tree_matmul_all_reduce(x2d, self.weight.t(), group, leaf=leaf)
     else:
-        output = matmul_tp_persistent(x2d, self.weight.t())
+        output = matmul_tp_persistent(x2d, self.weight.t(), leaf=leaf)
     output = output.reshape(*lead, output.shape[-1])
 
     if (not self.skip_bias_add) and self.bias is not None:
@@ -62,6 +82,11 @@ def patch_row_linear():
     RowParallelLinear.forward = _forward
 
 
-def patch_tp_invariant():
+def patch_tp_invariant(max_tp: int = 8):
+    """`max_tp` (extension): the largest TP degree that must reproduce the bits of all smaller ones."""
+    global MAX_TP
+    if max_tp < 1 or max_tp & (max_tp - 1):
+        raise ValueError("max_tp must be a power of two")
+    MAX_TP = max_tp
     patch_row_linear()
     print("Successfully patched vLLM to use custom tp_invariant implementation")

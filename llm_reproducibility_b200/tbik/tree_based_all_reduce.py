@@ -39,39 +39,55 @@ def tree_all_reduce_sum(x: torch.Tensor, device_group=None) -> torch.Tensor:
 
 _COMM_STREAMS = {}  # device index -> side stream the row blocks are reduced on
 
-# Row-block pipeline of `tree_matmul_all_reduce`: rows per block (a multiple of the 256-row GEMM tile: 2048 rows
-# x 4096 columns are exactly four waves of 256x128 tiles on 64 CTA pairs) and the CTAs left to the all-reduce
-# while a GEMM runs beside it.
-_PIPE_ROWS = int(os.environ.get("TBIK_PIPELINE_ROWS", "2048"))
-_PIPE_COMM_CTAS = int(os.environ.get("TBIK_PIPELINE_COMM_CTAS", "20"))
+# Row-block pipeline of `tree_matmul_all_reduce`.  Measured on two B200s (M = 8192, N = 4096, K per rank 2048 and
+# 6144): an all-reduce launch costs about 25 us of barriers and launch latency whatever its size, a GEMM cut into
+# blocks loses a few per cent per cut, and an all-reduce that runs beside a GEMM moves its bytes 35 - 80 % slower
+# than alone (both kernels' traffic meets in the peers' memory systems).  What survives: two equal blocks, 32 CTAs
+# for the all-reduce beside the second GEMM (fewer CTAs lose link rate, more starve the GEMM), and only where GEMM
+# and all-reduce take about equally long (o_proj at TP = 2: 243 -> 222 us; down_proj at TP = 2, three times more
+# GEMM than all-reduce: no cut beat GEMM-then-all-reduce, 417 us).
+_PIPE_MIN_ROWS = 1024      # shortest block worth a launch of its own
+_PIPE_COMM_CTAS = 32
+_PIPE_FORCE = None         # tests: (block_rows, comm_ctas) to use instead of the plan below
 
 
-def _pipeline_blocks(M: int, N: int, K_local: int, world: int) -> int:
-    """How many row blocks to cut the layer into (1 = no pipelining).
+def _estimates(M: int, N: int, K_local: int, world: int):
+    """(GEMM, all-reduce) seconds for one layer on one rank: 1.15 PFLOP/s plus 5 us for the GEMM; 25 us plus the
+    bytes that cross NVLink at 700 GB/s for the all-reduce (S at two ranks, 2 (n-1)/n S beyond)."""
+    t_gemm = 2.0 * M * N * K_local / 1.15e15 + 5e-6
+    S = M * N * 2
+    t_ar = 25e-6 + (S if world == 2 else 2.0 * (world - 1) / world * S) / 700e9
+    return t_gemm, t_ar
 
-    Batch invariance makes the cut free of numerical consequences: a row of C does not depend on which other
-    rows are computed with it.  Pipelining pays when the GEMM of a block takes about as long as its all-reduce,
-    so that one hides the other; when the all-reduce dominates (short K per rank, many ranks) one large message
-    is cheaper than several small ones.  Estimates: 1.2 PFLOP/s for the GEMM, 500 GB/s of bus bandwidth."""
+
+def _pipeline_plan(M: int, N: int, K_local: int, world: int):
+    """(rows of each block, CTAs for the all-reduce beside a GEMM), or None for "GEMM, then one all-reduce".
+
+    Two blocks: while the second block's GEMM runs on most of the SMs, the first block's all-reduce runs on the
+    rest; the second block's all-reduce then has the GPU to itself.  Batch invariance makes the cut free of
+    numerical consequences: a row of C does not depend on which other rows are computed with it."""
     mode = os.environ.get("TBIK_PIPELINE", "auto")
-    if mode == "0" or world < 2 or M < 2 * _PIPE_ROWS:
-        return 1
+    if mode == "0" or world < 2 or M < 2 * _PIPE_MIN_ROWS or N % 8:
+        return None
+    if _PIPE_FORCE is not None:
+        return _PIPE_FORCE
     if mode != "1":
-        t_gemm = 2.0 * M * N * K_local / 1.2e15
-        t_ar = 2.0 * (world - 1) / world * M * N * 2 / 500e9
-        if t_gemm < 0.5 * t_ar:
-            return 1
-    return -(-M // _PIPE_ROWS)
+        t_gemm, t_ar = _estimates(M, N, K_local, world)
+        if not (0.4 * t_ar <= t_gemm <= 1.5 * t_ar):
+            return None
+    first = -(-(M // 2) // 256) * 256
+    return [first, M - first], _PIPE_COMM_CTAS
 
 
-def tree_matmul_all_reduce(A: torch.Tensor, B: torch.Tensor, device_group=None) -> torch.Tensor:
+def tree_matmul_all_reduce(A: torch.Tensor, B: torch.Tensor, device_group=None, leaf=None) -> torch.Tensor:
     """Row-split layer in one call: this rank's tree matmul, then the tree all-reduce.
 
     Same bits as `tree_all_reduce_sum(matmul_tp_persistent(A, B), group)`.  The GEMM writes its partial
     result directly into the IPC-registered buffer the peers read from (no staging copy), then the tree
     all-reduce kernel runs.  Large calls are cut into blocks of rows: block i is reduced on a side stream by a
     few CTAs while the remaining CTAs multiply block i + 1, so most of the NVLink time hides behind the
-    tensor-core time (the partial sums of different rows never meet, so the cut cannot change a bit)."""
+    tensor-core time (the partial sums of different rows never meet, so the cut cannot change a bit).
+    `leaf` (extension): leaf width, the same on every rank and at every TP degree (see `leaf_for`)."""
     global custom_ar
     from .tree_based_matmul import matmul_tp_persistent
     if custom_ar is None:
@@ -83,37 +99,24 @@ def tree_matmul_all_reduce(A: torch.Tensor, B: torch.Tensor, device_group=None) 
         # under stream capture the buffer is usable as well: it was registered when the communicator was built
         view = custom_ar.registered_view((M, N), A.dtype)
     if view is None:
-        return tree_all_reduce_sum(matmul_tp_persistent(A, B), device_group)
+        return tree_all_reduce_sum(matmul_tp_persistent(A, B, leaf=leaf), device_group)
     capturing = A.is_cuda and torch.cuda.is_current_stream_capturing()
-    nblk = 1 if (capturing or custom_ar._IS_CAPTURING) else _pipeline_blocks(M, N, A.shape[1], custom_ar.world_size)
-    if nblk == 1:
-        matmul_tp_persistent(A, B, out=view)
+    plan = None if (capturing or custom_ar._IS_CAPTURING) else _pipeline_plan(M, N, A.shape[1], custom_ar.world_size)
+    if plan is None:
+        matmul_tp_persistent(A, B, out=view, leaf=leaf)
         if custom_ar._IS_CAPTURING and not capturing:
             return torch.zeros_like(view)  # warm-up run before a capture: only the shape matters
         return custom_ar.all_reduce(view, registered=True)
     dev = A.device
-    main = torch.cuda.current_stream(dev)
     comm = _COMM_STREAMS.get(dev.index)
     if comm is None:
         comm = _COMM_STREAMS[dev.index] = torch.cuda.Stream(device=dev, priority=-1)
-    out = torch.empty((M, N), device=dev, dtype=A.dtype)
-    sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    gemm_ctas = max(2, sms - _PIPE_COMM_CTAS)
-    rows = -(-M // nblk)
-    rows = -(-rows // 256) * 256
-    r0 = 0
-    while r0 < M:
-        r1 = min(M, r0 + rows)
-        last = r1 == M
-        # the first block has the GPU to itself; the later ones leave SMs to the all-reduce of their predecessor
-        matmul_tp_persistent(A[r0:r1], B, out=view[r0:r1], max_ctas=0 if r0 == 0 else gemm_ctas)
-        ready = main.record_event()
-        with torch.cuda.stream(comm):
-            comm.wait_event(ready)
-            custom_ar.tree_all_reduce_rows(view[r0:r1], out[r0:r1], max_blocks=0 if last else _PIPE_COMM_CTAS)
-        r0 = r1
-    main.wait_stream(comm)
-    return out
+    from ..mini_allreduce import custom_all_reduce_ops as ops
+    # one native call enqueues all blocks: GEMMs on the current stream, all-reduces on the side stream, the
+    # events between them, and the final join (the current stream waits for the last all-reduce)
+    block_rows, comm_ctas = plan
+    return ops.row_split_layer(custom_ar._ptr, A, B, custom_ar.buffer_ptrs[custom_ar.rank], custom_ar.max_size,
+                               block_rows, comm_ctas, comm.cuda_stream, leaf or 0)
 
 
 def tree_all_reduce_sum_native(x: torch.Tensor, device_group=None) -> torch.Tensor:

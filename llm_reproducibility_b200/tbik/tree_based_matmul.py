@@ -26,6 +26,26 @@ def tree_shape(K: int, leaf: int):
     return T.value, F.value, L.value
 
 
+def leaf_for(K_total: int, max_tp: int = 8, dtype: torch.dtype = torch.bfloat16) -> int:
+    """Leaf width for a row-split layer whose FULL reduction length is `K_total`, such that every tensor-parallel
+    degree up to `max_tp` (a power of two) sees a whole, aligned subtree per rank -- and therefore every degree,
+    TP = 1 included, produces the same bits.
+
+    The reference fixes the leaf at 256 (src/tbik/tree_based_matmul.py:206-231) and asserts K % 256 == 0 per rank
+    (:240-243), which a Qwen3-32B down_proj (K = 25600) fails at TP = 8 (3200 columns per rank).  Here the leaf is
+    the widest of 256, 128, 64 that divides K_total / max_tp and whose tree has at least max_tp subtrees at one
+    level; all ranks and all TP degrees must call with the same K_total and max_tp."""
+    if max_tp < 1 or max_tp & (max_tp - 1):
+        raise ValueError("max_tp must be a power of two")
+    for leaf in ((_LEAF.get(dtype, 256)), 128, 64):
+        if K_total % (leaf * max_tp) != 0:
+            continue
+        _, _, L = tree_shape(K_total, leaf)
+        if (1 << (L - 1)) % max_tp == 0:
+            return leaf
+    raise ValueError(f"no leaf width of 256, 128 or 64 splits K = {K_total} into {max_tp} aligned subtrees")
+
+
 def _k_major_weight(B: torch.Tensor) -> torch.Tensor:
     """Return W[N,K] (K contiguous) holding B[K,N]'s values.
 

@@ -142,6 +142,31 @@ def _tree_all_reduce_within(fa: int, reg_base: int, byte_offset: int, out: torch
     _lib.check(rc, "tbik_ar_tree_allreduce_within")
 
 
+def _row_split_layer(fa: int, A: torch.Tensor, B: torch.Tensor, reg_base: int, reg_bytes: int, block_rows: List[int],
+                     comm_ctas: int, side_stream: int, leaf: int = 0) -> torch.Tensor:
+    """out = tree all-reduce over ranks of (A @ B), pipelined over blocks of rows (tbik_ar_row_split_layer).
+    `side_stream` is the raw handle of the stream the all-reduces run on."""
+    from ..tbik.tree_based_matmul import _DTYPE_CODE as GEMM_DTYPES, _LEAF, _workspace, prepare_operands
+    if A.dtype not in GEMM_DTYPES or B.dtype != A.dtype:
+        raise RuntimeError("row_split_layer supports bfloat16 and float16")
+    M, K = A.shape
+    N = B.shape[1]
+    leaf = leaf or _LEAF[A.dtype]
+    A2, W = prepare_operands(A, B)
+    out = torch.empty((M, N), device=A.device, dtype=A.dtype)
+    with torch.cuda.device(A.device):
+        stream = _stream_of(A)
+        L = _lib.lib()
+        ws = _workspace(A.device, stream, max(int(L.tbik_gemm_workspace_bytes(r, N, K, leaf)) for r in set(block_rows)))
+        rows_arr = (ctypes.c_int * len(block_rows))(*block_rows)
+        rc = L.tbik_ar_row_split_layer(fa, A2.data_ptr(), W.data_ptr(), out.data_ptr(), M, N, K, max(A2.stride(0), K),
+                                       max(W.stride(0), K), GEMM_DTYPES[A.dtype], leaf, reg_base, reg_bytes,
+                                       ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                                       rows_arr, len(block_rows), comm_ctas, stream, side_stream)
+    _lib.check(rc, "tbik_ar_row_split_layer")
+    return out
+
+
 def _trace(fa: int) -> List[int]:
     """Phase time stamps (ns) of the last launch, 8 per CTA, flattened (see tbik_ar_trace)."""
     cap = 320
@@ -189,6 +214,9 @@ def _register() -> None:
     lib.impl("status", _status, any_key)
     lib.define("tree_all_reduce_within(int fa, int reg_base, int byte_offset, Tensor! out) -> ()")
     lib.impl("tree_all_reduce_within", _tree_all_reduce_within, "CUDA")
+    lib.define("row_split_layer(int fa, Tensor A, Tensor B, int reg_base, int reg_bytes, int[] block_rows, "
+               "int comm_ctas, int side_stream, int leaf=0) -> Tensor")
+    lib.impl("row_split_layer", _row_split_layer, "CUDA")
     lib.define("trace(int fa) -> int[]")
     lib.impl("trace", _trace, any_key)
     lib.define("tree_matmul(Tensor A, Tensor B, Tensor? bias=None) -> Tensor")
@@ -234,6 +262,10 @@ def meta_size(*args, **kwargs):
 
 def tree_all_reduce_within(*args, **kwargs):
     return torch.ops.tbik_kernel.tree_all_reduce_within.default(*args, **kwargs)
+
+
+def row_split_layer(*args, **kwargs):
+    return torch.ops.tbik_kernel.row_split_layer.default(*args, **kwargs)
 
 
 def trace(*args, **kwargs):

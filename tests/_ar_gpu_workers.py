@@ -139,6 +139,22 @@ def graph_capture(rank, world):
     torch.cuda.synchronize()
     ar.check_status()
     assert torch.equal(bits(out), bits(want))
+    # deferred registration: under capture an input that was never registered is taken as it is (no staging copy);
+    # its peers' addresses are exchanged when the capture block ends and patched into the reserved slot
+    from llm_reproducibility_b200.mini_allreduce import custom_all_reduce_ops as ops
+    with ar.capture():
+        with torch.cuda.stream(stream):
+            graph2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph2, stream=stream):
+                out2 = ar.all_reduce(static_in, registered=True)
+            handles, offsets = ops.get_graph_buffer_ipc_meta(ar._ptr)
+            assert len(offsets) == 1 and len(handles) == 64
+    dist.barrier()
+    for _ in range(3):
+        graph2.replay()
+    torch.cuda.synchronize()
+    ar.check_status()
+    assert torch.equal(bits(out2), bits(want))
     dist.barrier()
     ar.close()
     return True
@@ -295,13 +311,20 @@ def pipelined_layer(rank, world):
         W = (torch.randn(N, K, generator=g, device=device) * 0.02).to(torch.bfloat16)
         ks = K // world
         Xr, Wr = X[:, rank * ks:(rank + 1) * ks], W[:, rank * ks:(rank + 1) * ks]
-        assert tar._pipeline_blocks(M, N, ks, world) >= 2
+        assert tar._pipeline_plan(M, N, ks, world) is not None
         want = matmul_tp_persistent(X, W.t())
         for _ in range(3):
             got = tar.tree_matmul_all_reduce(Xr, Wr.t(), None)
         torch.cuda.synchronize()
         tar.custom_ar.check_status()
         assert torch.equal(bits(got), bits(want)), (M, K, N)
+        # other cuts: four blocks, a ragged last block, fewer CTAs for the all-reduce
+        for forced in (([1024] * (M // 1024 - 1) + [M - 1024 * (M // 1024 - 1)], 20), ([M - 300, 300], 8)):
+            tar._PIPE_FORCE = forced
+            got = tar.tree_matmul_all_reduce(Xr, Wr.t(), None)
+            torch.cuda.synchronize()
+            assert torch.equal(bits(got), bits(want)), (M, K, N, forced)
+        tar._PIPE_FORCE = None
         os.environ["TBIK_PIPELINE"] = "0"
         plain = tar.tree_matmul_all_reduce(Xr, Wr.t(), None)
         os.environ["TBIK_PIPELINE"] = "1"

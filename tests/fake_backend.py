@@ -86,7 +86,7 @@ class FakeOps:
     """Replaces mini_allreduce.custom_all_reduce_ops (the 8 reference functions + configure/status)."""
     IS_CUSTOM_AR_AVAILABLE = True
     CFG_SCRATCH_BYTES, CFG_ONESHOT_MAX_BYTES, CFG_MAX_BLOCKS, CFG_WAIT_LIMIT_NS, CFG_THREADS = 1, 2, 3, 4, 5
-    CFG_PUSH_MIN_BYTES, CFG_PUSH_CHUNKS, CFG_VEC_PACKS, CFG_LOADS_IN_FLIGHT, CFG_TRACE = 6, 7, 8, 9, 10
+    CFG_PUSH_MIN_BYTES, CFG_PUSH_CHUNKS, CFG_VEC_PACKS, CFG_LOADS_IN_FLIGHT, CFG_TRACE, CFG_CLUSTER_PAIRS = 6, 7, 8, 9, 10, 11
 
     def __init__(self, group):
         self.group = group

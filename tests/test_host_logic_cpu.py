@@ -72,7 +72,7 @@ def test_k_slab_plan_queries_need_no_gpu():
     for tiling in range(1, 7):
         sizes = [need(M, N, K, 256, tiling, s) for s in (2, 4, 8, 16)]
         assert all(b >= s * M * N * 2 for b, s in zip(sizes, (2, 4, 8, 16))), (tiling, sizes)   # room for every root
-        assert sizes == sorted(sizes)
+        assert all(b % 16 == 0 for b in sizes)
         assert need(M, N, K, 256, tiling, 32) == 0   # more than 16 slabs
         assert need(M, N, K, 256, tiling, 3) == 0    # not a power of two
     assert need(M, N, 1536, 256, 1, 4) == 0          # T = 6, F = 3: only two whole subtrees
