@@ -129,12 +129,6 @@ TBIK_DEVICE void tma_store_2d(const void* tmap, uint32_t smem_src, int32_t x, in
 TBIK_DEVICE void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // All bulk stores committed by this thread have finished READING shared memory.
 TBIK_DEVICE void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-// All bulk stores committed by this thread are complete (their global writes performed).
-TBIK_DEVICE void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-// Named barrier over `count` threads (a multiple of 32), separate from __syncthreads' barrier 0.
-TBIK_DEVICE void named_barrier_sync(uint32_t id, uint32_t count) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
 
 // ---------------------------------------------------------------- tcgen05 / TMEM
 TBIK_DEVICE void tmem_alloc(uint32_t smem_result, uint32_t ncols) {
@@ -259,15 +253,6 @@ TBIK_DEVICE void cluster_sync_all() {
 // Arrive on an mbarrier that may live in the other CTA of the cluster.
 TBIK_DEVICE void mbar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
-}
-
-// Tiled load issued by one CTA of a pair into its own shared memory; the bytes are accounted on
-// `cluster_bar`, which may be the partner's barrier.  One destination CTA only.
-TBIK_DEVICE void tma_load_2d_pair(uint32_t smem_dst, const void* tmap, int32_t x, int32_t y, uint32_t cluster_bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(cluster_bar), "r"(x), "r"(y)
-      : "memory");
 }
 
 TBIK_DEVICE void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols) {

@@ -45,7 +45,8 @@ _COMM_STREAMS = {}  # device index -> side stream the row blocks are reduced on
 # than alone (both kernels' traffic meets in the peers' memory systems).  What survives: two equal blocks, 32 CTAs
 # for the all-reduce beside the second GEMM (fewer CTAs lose link rate, more starve the GEMM), and only where GEMM
 # and all-reduce take about equally long (o_proj at TP = 2: 243 -> 222 us; down_proj at TP = 2, three times more
-# GEMM than all-reduce: no cut beat GEMM-then-all-reduce, 417 us).
+# GEMM than all-reduce: no cut beat GEMM-then-all-reduce, 417 us; down_proj at TP = 8, half as much GEMM as
+# all-reduce: 284 us either way).
 _PIPE_MIN_ROWS = 1024      # shortest block worth a launch of its own
 _PIPE_COMM_CTAS = 32
 _PIPE_FORCE = None         # tests: (block_rows, comm_ctas) to use instead of the plan below
@@ -73,7 +74,7 @@ def _pipeline_plan(M: int, N: int, K_local: int, world: int):
         return _PIPE_FORCE
     if mode != "1":
         t_gemm, t_ar = _estimates(M, N, K_local, world)
-        if not (0.4 * t_ar <= t_gemm <= 1.5 * t_ar):
+        if not (0.7 * t_ar <= t_gemm <= 1.5 * t_ar):
             return None
     first = -(-(M // 2) // 256) * 256
     return [first, M - first], _PIPE_COMM_CTAS

@@ -94,8 +94,13 @@ def test_normal_operands_within_one_ulp_of_reference_kernel(M, K, N, record_prop
     assert max_ulp <= MAX_ULP
 
 
-def test_fp16_integer_operands_bit_equal_to_reference_kernel():
+@pytest.mark.parametrize("M,K,N", [(192, 3072, 384), (200, 3072, 256), (100, 6144, 128)])
+def test_fp16_integer_operands_bit_equal_to_reference_kernel(M, K, N):
+    """fp16, radix-3 trees, ragged M.  N stays a multiple of the reference's 128-column tile: at other N the
+    GPU-compiled reference kernel (triton 3.6.0, sm_100) was observed to differ from its own CPU-interpreter run --
+    and from the oracle, which this repository's kernel matches there -- in a few hundred elements of columns 1..7,
+    so such shapes cannot serve as a comparison."""
     from llm_reproducibility_b200.tbik.tree_based_matmul import matmul_tp_persistent
     ref = reference_matmul()
-    A, W = operands(200, 3072, 320, torch.float16, 7, integer=True)
+    A, W = operands(M, K, N, torch.float16, 7, integer=True)
     assert torch.equal(matmul_tp_persistent(A, W.t()).view(torch.int16), ref(A, W.t()).view(torch.int16))
