@@ -866,7 +866,10 @@ struct Plan {
   size_t partial_off;     // offset of the slab roots in the workspace (0 when splits == 1)
   size_t partial_bytes;   // [splits][M][N rounded up to 8] elements
   bool valid;
-  size_t total_bytes() const { return splits > 1 ? partial_off + partial_bytes : scratch_bytes; }
+  size_t total_bytes() const {
+    if (splits > 1) return partial_off + partial_bytes;
+    return scratch_bytes > 0 ? scratch_off + scratch_bytes : 0;
+  }
 };
 
 static int log2_int(int v) {
@@ -898,10 +901,12 @@ static Plan make_plan(int tiling, int M, int N, int L, int max_ctas, int splits 
   pl.grid = v.pair ? 2 * units : units;
   pl.scratch_levels = (L - 1) > v.levels_on_chip ? (L - 1) - v.levels_on_chip : 0;
   pl.scratch_bytes = static_cast<size_t>(pl.grid) * pl.scratch_levels * v.level_bytes;
+  // The head of every workspace belongs to the arrival counters, whether this launch uses them or not: a launch
+  // that put its stack levels there would leave them non-zero for the next K-slab launch on the same workspace.
+  pl.scratch_off = kCounterBytes;
   if (splits > 1) {
     // one arrival counter per 128-row block of an output tile
     if (static_cast<size_t>(pl.tiles_m) * pl.tiles_n * (v.pair ? 2 : 1) * sizeof(uint32_t) > kCounterBytes) pl.valid = false;
-    pl.scratch_off = kCounterBytes;
     pl.partial_off = (pl.scratch_off + pl.scratch_bytes + 255) & ~size_t(255);
     pl.partial_bytes = static_cast<size_t>(splits) * M * ((N + 7) / 8 * 8) * 2;
   }
@@ -951,7 +956,7 @@ static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int ma
   for (int i = 0; i < 4; ++i) {
     if (!short_k && order[i] == 4) continue;  // long K: 256x256 only adds scratch need
     Plan pl = make_plan(order[i], M, N, L, max_ctas);
-    if (pl.scratch_bytes > 0 && !(have_ws && pl.scratch_bytes <= ws_bytes)) continue;
+    if (pl.total_bytes() > 0 && !(have_ws && pl.total_bytes() <= ws_bytes)) continue;
     const Variant& pv = kVariants[order[i] - 1][pl.deep ? 1 : 0];
     if (pl.tiles_m * pl.tiles_n * (pv.pair ? 2 : 1) >= enough) return pl;  // enough rows of C
   }
@@ -1033,7 +1038,7 @@ static int gemm_launch_plan(const void* A, const void* W, void* C, int M, int N,
   p.tiles_m = pl.tiles_m;
   p.tiles_n = pl.tiles_n;
   p.group_m = v.pair ? 8 : 16;  // 2048 rows of A per group: a wave of CTAs covers a near-square block of C
-  p.scratch = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) + pl.scratch_off);
+  p.scratch = workspace ? reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) + pl.scratch_off) : nullptr;
   p.scratch_levels = pl.scratch_levels;
   p.status = status_address(dev);
 

@@ -6,6 +6,8 @@ with any object that has the layer's attributes; `patch_row_linear` binds it to 
 """
 from __future__ import annotations
 
+import logging
+import os
 from typing import Callable, Optional
 
 import torch
@@ -13,10 +15,13 @@ import torch
 from ..tbik.tree_based_all_reduce import tree_matmul_all_reduce
 from ..tbik.tree_based_matmul import leaf_for, matmul_tp_persistent
 
+logger = logging.getLogger(__name__)
+
 # Largest tensor-parallel degree whose results must agree bit for bit with every smaller one (TP = 1 included).
 # It fixes the leaf width of every row-split layer from the layer's FULL K, so that engines started with
 # different TP degrees walk the same reduction tree.  Set through `patch_tp_invariant(max_tp=...)`.
 MAX_TP = 8
+CALLS = 0  # forwards served by `row_parallel_forward` in this process (lets an end-to-end run prove the patch is live)
 
 
 def layer_leaf(K_total: int, tp_size: int, dtype: torch.dtype) -> int:
@@ -39,6 +44,11 @@ def row_parallel_forward(self, input_, *, device_group_fn: Optional[Callable] = 
     Attributes used (those of vLLM's layer): input_is_parallel, tp_size, tp_rank, weight [N, K/tp],
     bias, skip_bias_add, reduce_results, return_bias, quant_method.
     """
+    global CALLS
+    CALLS += 1
+    if CALLS == 1:
+        logger.info("tree row-parallel forward active in process %d (tp rank %d of %d)", os.getpid(), self.tp_rank,
+                    self.tp_size)
     if self.input_is_parallel:
         input_parallel = input_
     else:
@@ -57,6 +67,15 @@ def row_parallel_forward(self, input_, *, device_group_fn: Optional[Callable] = 
     if self.reduce_results and self.tp_size > 1:
         group = device_group_fn() if device_group_fn is not None else None
         output = tree_matmul_all_reduce(x2d, self.weight.t(), group, leaf=leaf)
+        if os.environ.get("TBIK_VERIFY") == "1":
+            # debugging aid: the same layer through the library collective (all_gather + ordered adds)
+            from ..tbik.tree_based_all_reduce import tree_all_reduce_sum_native
+            want = tree_all_reduce_sum_native(matmul_tp_persistent(x2d, self.weight.t(), leaf=leaf), group)
+            bad = int((want.view(torch.int16) != output.view(torch.int16)).sum())
+            if bad or CALLS <= 8:
+                print(f"[tbik verify] pid {os.getpid()} rank {self.tp_rank} call {CALLS} x {tuple(x2d.shape)} "
+                      f"strides {tuple(x2d.stride())} w {tuple(self.weight.shape)} leaf {leaf}: {bad} mismatching elements",
+                      flush=True)
     else:
         output = matmul_tp_persistent(x2d, self.weight.t(), leaf=leaf)
     output = output.reshape(*lead, output.shape[-1])

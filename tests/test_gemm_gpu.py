@@ -309,6 +309,42 @@ def test_k_slabs_give_the_same_bits(M, K, N):
     assert torch.equal(bits(_gemm_slabs(h, Wh, M, N, K, 3, 2, dtype_code=1)), bits(one))
 
 
+def test_stack_scratch_and_k_slabs_share_one_workspace():
+    """A launch that keeps tree levels in the workspace (256-column tilings) followed, on the SAME workspace, by a
+    decode-sized launch that counts K-slab arrivals at its head: the first must not leave the counters non-zero.
+    (Found under a serving engine: the profile run of 4096 rows used the scratch, the decode steps after it
+    returned garbage.)"""
+    from llm_reproducibility_b200 import _lib
+    L = _lib.lib()
+    ws = torch.zeros(64 << 20, dtype=torch.uint8, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(11)
+    K, N = 1536, 1024
+    W = (torch.randn(N, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    s = torch.cuda.current_stream().cuda_stream
+
+    def ws_call(A, leaf, tiling=None):
+        M = A.shape[0]
+        C = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        if tiling is None:
+            rc = L.tbik_gemm_ws(A.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K, K, K, N, 0, leaf, 0, ws.data_ptr(), ws.numel(), s)
+        else:
+            rc = L.tbik_gemm_ex(A.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K, K, K, N, 0, leaf, 0, 0, tiling, ws.data_ptr(), ws.numel(), s)
+        assert rc == 0, _lib.last_error()
+        torch.cuda.synchronize()
+        return C
+
+    for leaf in (128, 256):
+        big = torch.randn(4096, K, generator=g, device="cuda").to(torch.bfloat16)
+        small = torch.randn(4, K, generator=g, device="cuda").to(torch.bfloat16)
+        want = _gemm_ex(small, W, 4, N, K, 0, 1, leaf=leaf)       # 128x128 tiling, its own workspace
+        for tiling in (None, 3, 4):                                # automatic, 128x256, 256x256: stack levels in scratch
+            ws_call(big, leaf, tiling)
+            for _ in range(2):
+                assert torch.equal(bits(ws_call(small, leaf)), bits(want)), (leaf, tiling)
+    from llm_reproducibility_b200.tbik.tree_based_matmul import gemm_device_status
+    assert gemm_device_status()[0] == 0
+
+
 def test_k_slab_argument_errors():
     from llm_reproducibility_b200 import _lib
     L = _lib.lib()
