@@ -72,9 +72,14 @@ def worker(args) -> None:
     from llm_reproducibility_b200.patch import apply_patches
     apply_patches()  # this process; the spawned workers get it through the plugin entry point (PYTHONPATH)
     from vllm import LLM, SamplingParams
+    extra = {}
+    if args.graphs:
+        # whole-forward CUDA graphs for the decode steps, no compiler in between: the patched layer is captured
+        # as it is (GEMM into the registered buffer, tree all-reduce kernel) and replayed
+        extra["compilation_config"] = {"mode": 0, "cudagraph_mode": "FULL_DECODE_ONLY", "cudagraph_capture_sizes": [1, 2, 4, 8]}
     llm = LLM(model=args.model, tensor_parallel_size=args.tp, dtype="bfloat16", skip_tokenizer_init=True,
               enforce_eager=not args.graphs, max_model_len=512, gpu_memory_utilization=0.30, seed=0,
-              enable_prefix_caching=False, max_num_seqs=max(8, args.bs))
+              enable_prefix_caching=False, max_num_seqs=max(8, args.bs), **extra)
     sp = SamplingParams(temperature=0.0, max_tokens=args.tokens, logprobs=0, detokenize=False, ignore_eos=True)
     all_prompts = prompts(4)
     outs = []

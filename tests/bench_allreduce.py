@@ -3,9 +3,13 @@ against NCCL all_reduce and the all_gather + ordered-adds path, bf16, 8 KB ... 6
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         tests/bench_allreduce.py [--iters 20] [--warmup 5] [--max-mb 64] [--min-kb 8]
-                                 [--oneshot-max-kb K] [--max-blocks B] [--threads T] [--push-min-kb K] [--push-chunks C] [--only-p2p]
+                                 [--oneshot-max-kb K] [--max-blocks B] [--threads T] [--push-min-kb K] [--push-chunks C]
+                                 [--vec-packs V] [--loads L] [--trace] [--only-p2p]
 
---oneshot-max-kb / --max-blocks override the built-in schedule choice (for tuning sweeps).
+--oneshot-max-kb / --max-blocks / --threads / --vec-packs / --loads override the built-in choices (for tuning sweeps).
+--trace adds, per size, the medians over CTAs of the kernel's phase stamps (GPU timer): first barrier, reduce
+phase, middle barrier, gather phase -- the way a multi-rank kernel is profiled here, since ncu is never run on a
+multi-rank command.
 
 Counterpart of the reference's tests/bench_allreduce.py:19-135, with device timing (CUDA events, max
 over ranks) instead of wall clock and without the clone inside the timed region.
@@ -34,6 +38,9 @@ def main():
     ap.add_argument("--threads", type=int, default=0)
     ap.add_argument("--push-min-kb", type=int, default=0)
     ap.add_argument("--push-chunks", type=int, default=0)
+    ap.add_argument("--vec-packs", type=int, default=0)
+    ap.add_argument("--loads", type=int, default=0)
+    ap.add_argument("--trace", action="store_true")
     ap.add_argument("--only-p2p", action="store_true")
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -58,6 +65,30 @@ def main():
         ops.configure(ar._ptr, ops.CFG_THREADS, args.threads)
     if args.max_blocks:
         ops.configure(ar._ptr, ops.CFG_MAX_BLOCKS, args.max_blocks)
+    if args.vec_packs:
+        ops.configure(ar._ptr, ops.CFG_VEC_PACKS, args.vec_packs)
+    if args.loads:
+        ops.configure(ar._ptr, ops.CFG_LOADS_IN_FLIGHT, args.loads)
+    if args.trace:
+        ops.configure(ar._ptr, ops.CFG_TRACE, 1)
+
+    def phases():
+        """Medians over the CTAs of the last launch, microseconds."""
+        import statistics
+        tr = ops.trace(ar._ptr)
+        nb = len(tr) // 8
+        if nb == 0:
+            return None
+        b = [tr[8 * i: 8 * i + 8] for i in range(nb)]
+        med = lambda xs: statistics.median(xs) / 1e3
+        out = {"ctas": nb, "kernel_us": (max(x[4] for x in b) - min(x[0] for x in b)) / 1e3,
+               "first_barrier_us": med([x[1] - x[0] for x in b]), "reduce_us": med([x[2] - x[1] for x in b])}
+        if all(x[3] for x in b):   # two-shot: a middle barrier, then the gather
+            out["middle_barrier_us"] = med([x[3] - x[2] for x in b])
+            out["gather_us"] = med([x[4] - x[3] for x in b])
+        else:
+            out["tail_us"] = med([x[4] - x[2] for x in b])
+        return out
 
     def timed(fn):
         for _ in range(args.warmup):
@@ -92,6 +123,8 @@ def main():
         if not args.only_p2p:
             res["nccl_allreduce_us"] = timed(lambda: dist.all_reduce(nccl_buf))
             res["allgather_adds_us"] = timed(lambda: tree_all_reduce_sum_native(x, None))
+        if args.trace:
+            res["phases_registered"] = phases()
         t = res["tree_p2p_registered_us"] * 1e-6
         res["algbw_GBs"] = nbytes / t / 1e9
         res["busbw_GBs"] = nbytes * 2 * (world - 1) / world / t / 1e9
