@@ -76,6 +76,10 @@ def _workspace(device: torch.device, stream: int, nbytes: int) -> Optional[torch
 
 _WS_NEED = {}  # (device index, M, N, K, leaf) -> bytes of scratch the automatic schedule wants
 
+# raw handle of the current stream of a device: the private fast getter when this torch has it (a fraction of a
+# microsecond), the public API otherwise (several microseconds per call, which is felt at decode sizes)
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None) or (lambda index: torch.cuda.current_stream(index).cuda_stream)
+
 
 def _launch(A, W, C, M, N, K, leaf, dev, max_ctas=0) -> int:
     """Enqueue the GEMM on the current stream of `dev` (which must be the current device)."""
@@ -84,7 +88,7 @@ def _launch(A, W, C, M, N, K, leaf, dev, max_ctas=0) -> int:
     need = _WS_NEED.get(key)
     if need is None:
         need = _WS_NEED[key] = int(L.tbik_gemm_workspace_bytes(M, N, K, leaf))
-    stream = torch.cuda.current_stream(dev).cuda_stream
+    stream = _raw_stream(dev.index)
     ws = _workspace(dev, stream, need)
     if max_ctas > 0:
         return L.tbik_gemm_ex(A.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K,
