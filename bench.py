@@ -368,6 +368,40 @@ def sustained_record(dom, dom_flops, local_rank, sustained_peak, seconds=2.0):
             "ms_times_mhz": (ms * c["sm_mhz"]) if c["sm_mhz"] else None}
 
 
+def fp32_nodes_record(sets, M, steps):
+    """The same step in the fp32-node mode (leaves and nodes fp32, one rounding at the root; leaf = K / 8): timed like
+    the headline, plus its mean error against fp64 on a sample of rows beside the default mode's."""
+    from llm_reproducibility_b200.tbik.tree_based_matmul import leaf_for_fp32_nodes, matmul_tp_persistent
+    nsets = len(sets)
+
+    def fstep(i):
+        for X, W, C in sets[i % nsets]:
+            matmul_tp_persistent(X, W.t(), out=C, leaf=leaf_for_fp32_nodes(X.shape[1], 8), node_dtype=torch.float32)
+    for i in range(3):
+        fstep(i)
+    torch.cuda.synchronize()
+    n = max(3, min(steps, 30))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(n):
+        fstep(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    rec = {"ms_per_step": ms, "tflops": step_flops(M) / (ms * 1e-3) / 1e12, "steps": n,
+           "leaf": [leaf_for_fp32_nodes(K, 8) for _, K, _ in LAYERS]}
+    # accuracy on 256 rows of the down_proj operands
+    X, W, _ = sets[0][-1]
+    Xs = X[:256]
+    exact = Xs.double() @ W.double().t()
+    d16 = matmul_tp_persistent(Xs, W.t())
+    d32 = matmul_tp_persistent(Xs, W.t(), leaf=leaf_for_fp32_nodes(X.shape[1], 8), node_dtype=torch.float32)
+    rec["mean_abs_err_vs_fp64"] = {"rounded_nodes": float((d16.double() - exact).abs().mean()),
+                                   "fp32_nodes": float((d32.double() - exact).abs().mean()),
+                                   "one_rounding_of_fp64": float((exact.to(torch.bfloat16).double() - exact).abs().mean())}
+    return rec
+
+
 def reference_triton_record(sets, M, steps):
     """The reference's own Triton kernel (src/tbik/tree_based_matmul.py, staged unmodified under oracle/_ref by
     oracle/build_ref.py) on this GPU and these operands: a comparator, never on the product's path."""
@@ -584,12 +618,13 @@ def main():
         cpu = {"value": v, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
                "sample": f"{rows} of {M} token rows of both layers, bf16, best of 3 ({secs:.2f} s per pass)"}
 
-    decode = sustained = ref_triton = probe = None
+    decode = sustained = ref_triton = probe = fp32_nodes = None
     if tp == 1 and not args.quick:
         sustained_peak, hbm_gbs, _ = load_other_peaks()
         decode = decode_record(dev, hbm_gbs)
         sustained = sustained_record(dom, dom_flops, local_rank, sustained_peak)
         ref_triton = reference_triton_record(sets, M, args.steps)
+        fp32_nodes = fp32_nodes_record(sets, M, args.steps)
     if tp > 1:
         probe = timeout_probe(rank, tp, dev)
         reset_communicator()
@@ -613,7 +648,7 @@ def main():
         if cpu is not None:
             line["cpu_baseline"] = cpu
         for key, val in (("parity_check", parity), ("timeout_probe", probe), ("decode", decode),
-                         ("sustained", sustained), ("reference_triton", ref_triton)):
+                         ("sustained", sustained), ("reference_triton", ref_triton), ("fp32_nodes", fp32_nodes)):
             if val is not None:
                 line[key] = val
         if ref_triton is not None and "tflops" in ref_triton:

@@ -35,7 +35,10 @@ extern "C" {
 
 /* Type of the tree nodes of the GEMM. */
 #define TBIK_NODE_INPUT 0 /* nodes rounded to the operand type: the reference's arithmetic   */
-#define TBIK_NODE_FP32 1  /* nodes kept in fp32, one final rounding                            */
+#define TBIK_NODE_FP32 1  /* leaves and nodes stay fp32 (one fp32 add per node, same tree); C, of the operand type,
+                             is the root rounded once                                                          */
+#define TBIK_NODE_FP32_OUT_FP32 2 /* as above, but C is an fp32 matrix (ldc in fp32 elements) holding the unrounded
+                             root: what a tensor-parallel rank hands to the cross-rank levels of the tree      */
 
 typedef void* tbik_stream_t; /* a cudaStream_t */
 
@@ -55,7 +58,13 @@ int tbik_tree_shape(int64_t K, int leaf, int* T, int* F, int* L);
  *       the reference's B = weight.t() without the transpose), row stride ldw; C row stride ldc.
  *   dtype       TBIK_DTYPE_BF16 or TBIK_DTYPE_FP16 (operands and C)
  *   leaf        leaf width in elements, multiple of 64 (the reference uses 256)
- *   node_dtype  TBIK_NODE_INPUT
+ *   node_dtype  TBIK_NODE_INPUT: the reference's arithmetic (every node rounded to the operand type).
+ *               TBIK_NODE_FP32 / TBIK_NODE_FP32_OUT_FP32: nothing is rounded below the root.  The tree (shape and
+ *               order) is the same function of (K, leaf), so batch- and TP-invariance hold exactly as before, but the
+ *               bits are not the reference's; accuracy against fp64 improves by an order of magnitude.  With fp32
+ *               nodes the leaf may be long (K / 8, say): fewer accumulator drains.  The tree's stack then lives in
+ *               tensor memory only: at most 3 levels on the full-rate 128-column tilings (7 / 15 on the 64- / 32-column
+ *               ones), no K-slabs; deeper trees are refused -- use a wider leaf.
  * A and W must be 16-byte aligned with lda, ldw multiples of 8.  M == 0 or N == 0 is a no-op.
  * The kernel is enqueued on `stream`.  This entry point uses no scratch memory and allocates
  * nothing: it picks among the tilings whose tree stack fits on chip (128-column tiles: trees of up to
@@ -203,6 +212,15 @@ int tbik_ar_tree_allreduce(tbik_ar_t comm, const void* inp, void* out, int64_t n
  * Replaces: the same reference functions as tbik_ar_tree_allreduce, minus the copy at custom_all_reduce.cu:112-114. */
 int tbik_ar_tree_allreduce_within(tbik_ar_t comm, const void* reg_base, size_t byte_offset, void* out, int64_t numel,
                                   int dtype, tbik_stream_t stream);
+
+/* Tree all-reduce of fp32 contributions with ONE rounding at the end: out[numel] (out_dtype: TBIK_DTYPE_BF16 or
+ * TBIK_DTYPE_FP16, 16-byte aligned) = round(rank-pair tree sum, in fp32, of every rank's numel floats at
+ * reg_base + byte_offset).  It finishes a tree whose nodes stay fp32 (tbik_gemm_ex with TBIK_NODE_FP32_OUT_FP32
+ * writes each rank's subtree root there): same tree as the TP = 1 launch with TBIK_NODE_FP32, hence the same bits.
+ * reg_base must be a registered buffer (tbik_ar_register_buffer); byte_offset a multiple of 32; numel a multiple
+ * of 8.  Collective.  No counterpart in the reference, whose nodes are always rounded to the operand type. */
+int tbik_ar_tree_allreduce_rounding(tbik_ar_t comm, const void* reg_base, size_t byte_offset, void* out, int64_t numel,
+                                    int out_dtype, tbik_stream_t stream);
 
 /* The row-split layer as a pipeline: out[M, N] (contiguous) = tree-all-reduce over ranks of (A * W^T), computed
  * block of rows by block of rows.  Block i's GEMM (tbik_gemm_ws arithmetic) writes its partial rows into the

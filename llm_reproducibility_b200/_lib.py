@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(PKG_DIR, "libtbik_b200.so")
 
 TBIK_OK = 0
 DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = 0, 1, 2
-NODE_INPUT, NODE_FP32 = 0, 1
+NODE_INPUT, NODE_FP32, NODE_FP32_OUT_FP32 = 0, 1, 2
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -43,6 +43,7 @@ _PROTOTYPES = {
     "tbik_ar_tree_allreduce": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp, _sz, _vp]),
     "tbik_ar_allreduce": (_i32, [_vp, _vp, _vp, _i64, _i32, _vp, _sz, _vp]),
     "tbik_ar_tree_allreduce_within": (_i32, [_vp, _vp, _sz, _vp, _i64, _i32, _vp]),
+    "tbik_ar_tree_allreduce_rounding": (_i32, [_vp, _vp, _sz, _vp, _i64, _i32, _vp]),
     "tbik_ar_row_split_layer": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i32, _i32, _vp, _sz, _vp, _sz,
                                         ctypes.POINTER(_i32), _i32, _i32, _vp, _vp]),
     "tbik_ar_trace": (_i32, [_vp, ctypes.POINTER(ctypes.c_uint64), _i32, ctypes.POINTER(_i32)]),

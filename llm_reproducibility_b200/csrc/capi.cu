@@ -118,6 +118,11 @@ int tbik_ar_tree_allreduce_within(tbik_ar_t comm, const void* reg_base, size_t b
   return tbik::ar_run_within(comm, reg_base, byte_offset, out, numel, dtype, static_cast<cudaStream_t>(stream));
 }
 
+int tbik_ar_tree_allreduce_rounding(tbik_ar_t comm, const void* reg_base, size_t byte_offset, void* out, int64_t numel,
+                                    int out_dtype, void* stream) {
+  return tbik::ar_run_rounding(comm, reg_base, byte_offset, out, numel, out_dtype, static_cast<cudaStream_t>(stream));
+}
+
 int tbik_ar_row_split_layer(tbik_ar_t comm, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
                             int64_t ldw, int dtype, int leaf, void* reg_base, size_t reg_bytes, void* workspace,
                             size_t workspace_bytes, const int* block_rows, int num_blocks, int comm_ctas,

@@ -37,6 +37,8 @@ int ar_run(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, vo
            bool tree, cudaStream_t stream);
 int ar_run_within(tbik_ar_t h, const void* reg_base, size_t byte_offset, void* out, int64_t numel, int dtype,
                   cudaStream_t stream);
+int ar_run_rounding(tbik_ar_t h, const void* reg_base, size_t byte_offset, void* out, int64_t numel, int out_dtype,
+                    cudaStream_t stream);
 int ar_row_split_layer(tbik_ar_t h, const void* A, const void* W, void* out, int M, int N, int K, int64_t lda,
                        int64_t ldw, int dtype, int leaf, void* reg_base, size_t reg_bytes, void* workspace,
                        size_t ws_bytes, const int* block_rows, int nblk, int comm_ctas, cudaStream_t main,

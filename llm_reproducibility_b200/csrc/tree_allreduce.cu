@@ -152,6 +152,39 @@ __device__ __forceinline__ void reduce_range(const RankData& dp, int64_t in_off,
   }
 }
 
+// All-gather of the two-shot schedules: every rank's part of the result is fetched from that rank's scratch.  Same
+// thread <-> same offset as in the reduce phase.  All NG loads of an offset (two offsets when the message is long
+// enough) are in flight before the first store: a load answered over NVLink takes microseconds, and a thread that
+// stored each vector before asking for the next one would move 16 bytes per round trip.
+template <int NG, int VEC>
+__device__ __forceinline__ void gather_parts(void* const (&scratch)[NG], void* out, int64_t part, int64_t last,
+                                             int64_t tid, int64_t stride) {
+  constexpr int GU = (NG >= 8 ? 2 : 4) / VEC;  // offsets per thread in flight: 16 packs of payload
+  int64_t idx = tid;
+  for (; idx + (GU - 1) * stride < part; idx += GU * stride) {
+    Vec<VEC> v[GU][NG];
+#pragma unroll
+    for (int u = 0; u < GU; ++u) {
+#pragma unroll
+      for (int src = 0; src < NG; ++src) v[u][src] = ld_vec<VEC>(scratch[src], idx + u * stride);
+    }
+#pragma unroll
+    for (int u = 0; u < GU; ++u) {
+#pragma unroll
+      for (int src = 0; src < NG; ++src) st_vec<VEC>(out, src * part + idx + u * stride, v[u][src]);
+    }
+  }
+  for (; idx < last; idx += stride) {
+    Vec<VEC> v[NG];
+#pragma unroll
+    for (int src = 0; src < NG; ++src)
+      if (src == NG - 1 || idx < part) v[src] = ld_vec<VEC>(scratch[src], idx);
+#pragma unroll
+    for (int src = 0; src < NG; ++src)
+      if (src == NG - 1 || idx < part) st_vec<VEC>(out, src * part + idx, v[src]);
+  }
+}
+
 template <typename T, int NG, bool TREE, int VEC, int UNROLL>
 __global__ void __launch_bounds__(kThreads, 1) allreduce_oneshot_kernel(const ArArgs a) {
   __shared__ uint32_t fail;
@@ -200,36 +233,70 @@ __global__ void __launch_bounds__(kThreads, 1) allreduce_twoshot_kernel(const Ar
   // release this rank's scratch writes / acquire the peers'
   if (!block_barrier<NG>(a.sg, a.self, rank, a.status, a.limit_ns, 2, &fail)) return;
   stamp(a, 3);
-  // all-gather: same thread <-> same offset in both phases.  All NG loads of an offset (two offsets when the
-  // message is long enough) are in flight before the first store: a load answered over NVLink takes
-  // microseconds, and a thread that stored each vector before asking for the next one would move 16 bytes
-  // per round trip.
-  void* out = a.out;
-  const int64_t last = a.nvec - part * (NG - 1);  // length of the last rank's part (>= part)
-  constexpr int GU = (NG >= 8 ? 2 : 4) / VEC;  // offsets per thread in flight: 16 packs of payload
-  int64_t idx = tid;
-  for (; idx + (GU - 1) * stride < part; idx += GU * stride) {
-    Vec<VEC> v[GU][NG];
+  // all-gather; `last` = length of the last rank's part (>= part)
+  gather_parts<NG, VEC>(scratch, a.out, part, a.nvec - part * (NG - 1), tid, stride);
+  stamp(a, 4);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// fp32 in, 16-bit out: the cross-rank levels of a tree whose nodes stay fp32.  Every rank contributes the fp32 root
+// of its subtree; the rank-pair tree adds them in fp32; the sum is rounded ONCE to OutT.  A vector is 8 floats
+// (one 256-bit load) and becomes one 16-byte pack of the result, so the two-shot schedule rounds in its reduce phase
+// and gathers half the bytes.
+template <typename OutT>
+__device__ __forceinline__ uint4 round_pack(const Vec<2>& v) {
+  float f[8];
+  f[0] = __uint_as_float(v.q[0].x); f[1] = __uint_as_float(v.q[0].y);
+  f[2] = __uint_as_float(v.q[0].z); f[3] = __uint_as_float(v.q[0].w);
+  f[4] = __uint_as_float(v.q[1].x); f[5] = __uint_as_float(v.q[1].y);
+  f[6] = __uint_as_float(v.q[1].z); f[7] = __uint_as_float(v.q[1].w);
+  return Elem<OutT>::down(f);
+}
+
+template <typename OutT, int NG, int UNROLL>
+__global__ void __launch_bounds__(kThreads, 1) allreduce_cast_oneshot_kernel(const ArArgs a) {
+  __shared__ uint32_t fail;
+  if (threadIdx.x == 0) fail = 0u;
+  stamp(a, 0);
+  const RankData dp = *a.dp;
+  if (!block_barrier<NG>(a.sg, a.self, a.rank, a.status, a.limit_ns, 1, &fail)) return;
+  stamp(a, 1);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  uint4* out = reinterpret_cast<uint4*>(a.out);
+  reduce_range<float, NG, true, 2, UNROLL>(dp, a.in_off, 0, a.nvec, tid, stride,
+                                           [&](int64_t i, const Vec<2>& v) { out[i] = round_pack<OutT>(v); });
+  stamp(a, 2);
+  if (a.keep_input == 0) block_barrier<NG>(a.sg, a.self, a.rank, a.status, a.limit_ns, 3, &fail);
+  stamp(a, 4);
+}
+
+template <typename OutT, int NG, int UNROLL>
+__global__ void __launch_bounds__(kThreads, 1) allreduce_cast_twoshot_kernel(const ArArgs a) {
+  __shared__ uint32_t fail;
+  if (threadIdx.x == 0) fail = 0u;
+  stamp(a, 0);
+  const RankData dp = *a.dp;
+  const int rank = a.rank;
+  const int64_t part = a.nvec / NG;
+  const int64_t start = rank * part;
+  const int64_t end = rank == NG - 1 ? a.nvec : start + part;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  void* scratch[NG];
 #pragma unroll
-    for (int u = 0; u < GU; ++u) {
-#pragma unroll
-      for (int src = 0; src < NG; ++src) v[u][src] = ld_vec<VEC>(scratch[src], idx + u * stride);
-    }
-#pragma unroll
-    for (int u = 0; u < GU; ++u) {
-#pragma unroll
-      for (int src = 0; src < NG; ++src) st_vec<VEC>(out, src * part + idx + u * stride, v[u][src]);
-    }
+  for (int r = 0; r < NG; ++r) scratch[r] = a.sg.sig[r] + 1;
+  if (!block_barrier<NG>(a.sg, a.self, rank, a.status, a.limit_ns, 1, &fail)) return;
+  stamp(a, 1);
+  {
+    uint4* mine = reinterpret_cast<uint4*>(scratch[rank]);
+    reduce_range<float, NG, true, 2, UNROLL>(dp, a.in_off, start, end, tid, stride,
+                                             [&](int64_t i, const Vec<2>& v) { mine[i - start] = round_pack<OutT>(v); });
   }
-  for (; idx < last; idx += stride) {
-    Vec<VEC> v[NG];
-#pragma unroll
-    for (int src = 0; src < NG; ++src)
-      if (src == NG - 1 || idx < part) v[src] = ld_vec<VEC>(scratch[src], idx);
-#pragma unroll
-    for (int src = 0; src < NG; ++src)
-      if (src == NG - 1 || idx < part) st_vec<VEC>(out, src * part + idx, v[src]);
-  }
+  stamp(a, 2);
+  if (!block_barrier<NG>(a.sg, a.self, rank, a.status, a.limit_ns, 2, &fail)) return;
+  stamp(a, 3);
+  gather_parts<NG, 1>(scratch, a.out, part, a.nvec - part * (NG - 1), tid, stride);
   stamp(a, 4);
 }
 
@@ -361,14 +428,8 @@ enum Schedule { kOneShot = 0, kTwoShot = 1, kPush = 2 };
 // `pairs`: launch the CTAs as clusters of two.  The kernels use no cluster feature; the point is placement: a
 // cluster occupies both SMs of a pair, so an all-reduce that runs beside a GEMM whose CTAs are themselves pairs
 // takes whole pairs away from it instead of halves of many.
-template <typename T, int NG, bool TREE, int VEC, int UNROLL>
-static int launch_kernel(const ArArgs& a, int sched, int blocks, int threads, cudaStream_t stream, bool pairs) {
-  void (*kernel)(const ArArgs) = allreduce_oneshot_kernel<T, NG, TREE, VEC, UNROLL>;
-  if (sched == kPush) {
-    if constexpr (NG >= 2) kernel = allreduce_push_kernel<T, NG, TREE, VEC, UNROLL>;
-  } else if (sched == kTwoShot) {
-    kernel = allreduce_twoshot_kernel<T, NG, TREE, VEC, UNROLL>;
-  }
+static int launch_fn(void (*kernel)(const ArArgs), const ArArgs& a, int blocks, int threads, cudaStream_t stream,
+                     bool pairs) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
   cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
@@ -386,6 +447,32 @@ static int launch_kernel(const ArArgs& a, int sched, int blocks, int threads, cu
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, a);
   if (e != cudaSuccess) return set_cuda_error(e, "all-reduce kernel launch");
   return TBIK_OK;
+}
+
+template <typename T, int NG, bool TREE, int VEC, int UNROLL>
+static int launch_kernel(const ArArgs& a, int sched, int blocks, int threads, cudaStream_t stream, bool pairs) {
+  void (*kernel)(const ArArgs) = allreduce_oneshot_kernel<T, NG, TREE, VEC, UNROLL>;
+  if (sched == kPush) {
+    if constexpr (NG >= 2) kernel = allreduce_push_kernel<T, NG, TREE, VEC, UNROLL>;
+  } else if (sched == kTwoShot) {
+    kernel = allreduce_twoshot_kernel<T, NG, TREE, VEC, UNROLL>;
+  }
+  return launch_fn(kernel, a, blocks, threads, stream, pairs);
+}
+
+// fp32 -> 16-bit variants: 16 packs of payload in flight per thread (8 for one and two ranks' worth of loads)
+template <typename OutT>
+static int launch_cast(int world, const ArArgs& a, int sched, int blocks, int threads, cudaStream_t stream, bool pairs) {
+  void (*kernel)(const ArArgs) = nullptr;
+  const bool two = sched == kTwoShot;
+  switch (world) {
+    case 1: kernel = allreduce_cast_oneshot_kernel<OutT, 1, 4>; break;
+    case 2: kernel = two ? allreduce_cast_twoshot_kernel<OutT, 2, 4> : allreduce_cast_oneshot_kernel<OutT, 2, 4>; break;
+    case 4: kernel = two ? allreduce_cast_twoshot_kernel<OutT, 4, 2> : allreduce_cast_oneshot_kernel<OutT, 4, 2>; break;
+    case 8: kernel = two ? allreduce_cast_twoshot_kernel<OutT, 8, 1> : allreduce_cast_oneshot_kernel<OutT, 8, 1>; break;
+    default: return set_error(TBIK_ERR_SHAPE, "tree all-reduce supports 1, 2, 4 or 8 ranks");
+  }
+  return launch_fn(kernel, a, blocks, threads, stream, pairs);
 }
 
 // `vec` = 16-byte packs per load instruction (1 or 2), `loads` = 16-byte packs a thread keeps in flight (0 = the
@@ -453,7 +540,7 @@ static int dispatch_world(int world, const ArArgs& a, int sched, int blocks, int
 // (or the stream is capturing).
 static int ar_run_impl(tbik_ar_t h, const void* inp, void* out, int64_t numel, int dtype, void* reg_buffer,
                        size_t reg_bytes, const void* reg_base, bool tree, cudaStream_t stream, int max_blocks = -1,
-                       bool keep_input = false) {
+                       bool keep_input = false, int cast_dtype = -1) {
   Communicator* c = as_comm(h);
   if (!c) return set_error(TBIK_ERR_ARG, "all-reduce: null communicator");
   if (c->status_host && c->status_host->w[0] != 0) c->poisoned = true;
@@ -468,6 +555,13 @@ static int ar_run_impl(tbik_ar_t h, const void* inp, void* out, int64_t numel, i
   const size_t bytes = static_cast<size_t>(numel) * esz;
   if (bytes % 16 != 0)
     return set_error(TBIK_ERR_SHAPE, "all-reduce requires the byte size to be a multiple of 16");
+  const bool cast = cast_dtype >= 0;
+  if (cast) {
+    // fp32 contributions, fp32 tree, one rounding to a 16-bit result: vectors of 8 elements
+    if (dtype != TBIK_DTYPE_FP32 || !tree || (cast_dtype != TBIK_DTYPE_BF16 && cast_dtype != TBIK_DTYPE_FP16))
+      return set_error(TBIK_ERR_DTYPE, "rounding all-reduce: float32 contributions, tree order, bfloat16 or float16 result");
+    if (numel % 8 != 0) return set_error(TBIK_ERR_SHAPE, "rounding all-reduce: the element count must be a multiple of 8");
+  }
   if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0) return set_error(TBIK_ERR_ALIGN, "all-reduce: out must be 16-byte aligned");
 
   const void* src = inp;
@@ -511,9 +605,13 @@ static int ar_run_impl(tbik_ar_t h, const void* inp, void* out, int64_t numel, i
   // two ranks: both schedules pull the same number of remote bytes, one-shot skips the scratch round trip
   // more ranks: measured on 8 GPUs, one-shot wins up to 1 MiB (26 vs 37 us at 512 KiB, 32 vs 38 us at 1 MiB), loses from 2 MiB
   if (one_max == 0) one_max = c->world <= 2 ? ~size_t(0) : (1u << 20);
+  // rounding variant on two ranks: the two-shot schedule pulls 3/4 of the one-shot's bytes (half the fp32
+  // contributions, then half the 16-bit result), which pays for its second barrier on long messages only
+  if (cast && c->oneshot_max_bytes == 0 && c->world == 2) one_max = 32u << 20;
   bool twoshot = c->world > 1 && bytes > one_max && c->full_nvlink;
   if (twoshot) {
-    const int64_t part = npacks / c->world + 2 * c->world;  // the last rank's part, in packs, rounded up
+    // the last rank's part of the result in 16-byte packs, rounded up (rounding variant: 8 elements per pack)
+    const int64_t part = (cast ? numel / 8 : npacks) / c->world + 2 * c->world;
     if (static_cast<size_t>(part) * 16 > c->scratch_bytes) {
       if (bytes <= (8u << 20)) twoshot = false;  // small enough for the one-shot schedule
       else return set_error(TBIK_ERR_SHAPE, "all-reduce: message needs more scratch than the meta buffer provides (raise max_size)");
@@ -529,8 +627,13 @@ static int ar_run_impl(tbik_ar_t h, const void* inp, void* out, int64_t numel, i
       if (push_chunks > part) push_chunks = part > 0 ? static_cast<int>(part) : 1;
     }
   }
+  if (cast) {
+    if (byte_off % 32 != 0 || (reinterpret_cast<uintptr_t>(src) & 31u) != 0)
+      return set_error(TBIK_ERR_ALIGN, "rounding all-reduce: the contributions must be 32-byte aligned");
+    push_chunks = 0;  // no push variant
+  }
   // 256-bit accesses when asked for and every address involved is 32-byte aligned
-  int vec = (c->vec_packs == 2 && dtype == TBIK_DTYPE_BF16 && tree && c->world >= 2) ? 2 : 1;
+  int vec = cast ? 2 : (c->vec_packs == 2 && dtype == TBIK_DTYPE_BF16 && tree && c->world >= 2) ? 2 : 1;
   if (vec == 2 && (npacks % 2 != 0 || byte_off % 32 != 0 || (reinterpret_cast<uintptr_t>(out) & 31u) != 0 ||
                    (reinterpret_cast<uintptr_t>(src) & 31u) != 0))
     vec = 1;
@@ -564,6 +667,9 @@ static int ar_run_impl(tbik_ar_t h, const void* inp, void* out, int64_t numel, i
   const int sched = push_chunks > 0 ? kPush : (twoshot ? kTwoShot : kOneShot);
   const int loads = c->loads_in_flight;
   const bool pairs = c->cluster_pairs != 0 && blocks % 2 == 0;
+  if (cast)
+    return cast_dtype == TBIK_DTYPE_BF16 ? launch_cast<__nv_bfloat16>(c->world, a, sched, blocks, threads, stream, pairs)
+                                         : launch_cast<__half>(c->world, a, sched, blocks, threads, stream, pairs);
   if (dtype == TBIK_DTYPE_FP32)
     return tree ? dispatch_world<float, true>(c->world, a, sched, blocks, threads, stream, vec, loads, pairs)
                 : dispatch_world<float, false>(c->world, a, sched, blocks, threads, stream, vec, loads, pairs);
@@ -584,6 +690,15 @@ int ar_run_within(tbik_ar_t h, const void* reg_base, size_t byte_offset, void* o
   if (!reg_base) return set_error(TBIK_ERR_ARG, "all-reduce: null registered buffer");
   return ar_run_impl(h, static_cast<const char*>(reg_base) + byte_offset, out, numel, dtype, nullptr, 0, reg_base, true,
                      stream);
+}
+
+int ar_run_rounding(tbik_ar_t h, const void* reg_base, size_t byte_offset, void* out, int64_t numel, int out_dtype,
+                    cudaStream_t stream) {
+  if (!reg_base) return set_error(TBIK_ERR_ARG, "all-reduce: null registered buffer");
+  if (out_dtype != TBIK_DTYPE_BF16 && out_dtype != TBIK_DTYPE_FP16)
+    return set_error(TBIK_ERR_DTYPE, "rounding all-reduce: the result is bfloat16 or float16");
+  return ar_run_impl(h, static_cast<const char*>(reg_base) + byte_offset, out, numel, TBIK_DTYPE_FP32, nullptr, 0,
+                     reg_base, true, stream, -1, false, out_dtype);
 }
 
 // Row-split layer as a pipeline over blocks of rows: the GEMM of block i + 1 runs on `main` while the tree

@@ -160,7 +160,10 @@ TBIK_DEVICE void combine_roots(const GemmParams& p, int row, int col0, int packs
 }
 
 // SLABS: the instantiation that serves K-slab launches (p.splits > 1); the plain one carries none of that code.
-template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR, bool SLABS>
+// NODE32: tree nodes stay fp32 (leaves are not rounded, every node is one fp32 add, the stack lives in tensor memory
+// as fp32 columns); OUT32: the root is stored as fp32 (a rank's subtree root on its way to the cross-rank levels),
+// otherwise it is rounded once to the operand type.
+template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR, bool SLABS, bool NODE32 = false, bool OUT32 = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_c, const GemmParams p) {
@@ -362,6 +365,14 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int kb = 0; kb < 4; ++kb) {
               if (!kblock(kb)) break;
             }
+          } else if ((p.kblocks_per_leaf & 3) == 0) {
+            // long leaves (fp32 nodes): four k-blocks of straight-line code per trip
+            for (int kb4 = 0; ok && kb4 < p.kblocks_per_leaf; kb4 += 4) {
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                if (!kblock(kb4 + u)) break;
+              }
+            }
           } else {
             for (int kb = 0; kb < p.kblocks_per_leaf; ++kb) {
               if (!kblock(kb)) break;
@@ -479,6 +490,124 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           // keep step with the two rendezvous of the draining warps' arrival protocol (below)
           epi_sync();
           if (ok) epi_sync();
+        }
+      }
+    } else if constexpr (NODE32) {
+      // ---------------------------------------------------------- fp32 nodes: nothing is rounded before the root
+      constexpr int CW = C_::COLS_PER_WARP;
+      float s0f[CW];  // the open level-0 group / the node that climbs the tree, fp32
+      auto stack_col = [&](int lvl, int c) -> uint32_t {
+        return tmem_base + lane_off + C_::TMEM_STACK_COL0 + static_cast<uint32_t>(lvl - 1) * BN + h * CW + c * CHUNK;
+      };
+      uint32_t leaf_ctr = 0;
+      for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
+        int tm, tn;
+        tile_coords(p, tile, tm, tn);
+        const int row = tm * TILE_M + static_cast<int>(cta_rank) * BM + q * 32 + lane;
+        int c0 = 0;
+        uint32_t g = 0;
+        for (int leaf = 0; ok && leaf < p.T; ++leaf, ++leaf_ctr) {
+          const uint32_t a = leaf_ctr & 1u;
+          const uint32_t aphase = (leaf_ctr >> 1) & 1u;
+          if (!mbar_wait_bounded(tfull_bar(a), aphase, abort_flag, WAIT_LIMIT_NS)) {
+            ok = false;
+            role_failed = 4;
+            break;
+          }
+          tc_fence_after_sync();
+          tmem_wait_st();  // stack stores of earlier leaves have landed
+          const uint32_t tacc = tmem_base + lane_off + a * BN + h * CW;
+          const bool add0 = c0 > 0;
+          {
+            uint32_t raw[2][32];
+            tmem_ld32(tacc, raw[0]);
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+              tmem_wait_ld();
+              if (c + 1 < NCH) {
+                tmem_ld32(tacc + (c + 1) * CHUNK, raw[(c + 1) & 1]);
+              } else {
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * a);  // accumulator may be overwritten now
+              }
+#pragma unroll
+              for (int j = 0; j < CHUNK; ++j) {
+                const float v = __uint_as_float(raw[c & 1][j]);
+                s0f[c * CHUNK + j] = add0 ? __fadd_rn(s0f[c * CHUNK + j], v) : v;  // level 0: radix F, sequential
+              }
+            }
+          }
+          if (++c0 < p.F) continue;
+          c0 = 0;
+          uint32_t gb = g++;
+          int lvl = 1;
+          while (lvl < p.L && (gb & 1u)) {
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+              uint32_t t[32];
+              tmem_ld32(stack_col(lvl, c), t);
+              tmem_wait_ld();
+#pragma unroll
+              for (int j = 0; j < CHUNK; ++j) s0f[c * CHUNK + j] = __fadd_rn(__uint_as_float(t[j]), s0f[c * CHUNK + j]);
+            }
+            gb >>= 1;
+            ++lvl;
+          }
+          if (lvl < p.L) {
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+              uint32_t t[32];
+#pragma unroll
+              for (int j = 0; j < CHUNK; ++j) t[j] = __float_as_uint(s0f[c * CHUNK + j]);
+              tmem_st32(stack_col(lvl, c), t);
+            }
+          } else if (row < p.M) {
+            // root of the tile's tree
+            if constexpr (OUT32) {
+              float* crow = reinterpret_cast<float*>(p.C) + static_cast<int64_t>(row) * p.ldc;
+              const bool vec32 = (p.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.C) & 15u) == 0);
+#pragma unroll
+              for (int c = 0; c < NCH; ++c) {
+                const int col0 = tn * BN + h * CW + c * CHUNK;
+                if (col0 >= p.N) continue;
+                if (vec32 && col0 + CHUNK <= p.N) {
+                  float4* dst = reinterpret_cast<float4*>(crow + col0);
+#pragma unroll
+                  for (int j = 0; j < CHUNK / 4; ++j)
+                    dst[j] = make_float4(s0f[c * CHUNK + 4 * j], s0f[c * CHUNK + 4 * j + 1], s0f[c * CHUNK + 4 * j + 2],
+                                         s0f[c * CHUNK + 4 * j + 3]);
+                } else {
+#pragma unroll
+                  for (int j = 0; j < CHUNK; ++j)
+                    if (col0 + j < p.N) crow[col0 + j] = s0f[c * CHUNK + j];
+                }
+              }
+            } else {
+              // the one rounding of this mode
+              T* crow = reinterpret_cast<T*>(p.C) + static_cast<int64_t>(row) * p.ldc;
+#pragma unroll
+              for (int c = 0; c < NCH; ++c) {
+                const int col0 = tn * BN + h * CW + c * CHUNK;
+                if (col0 >= p.N) continue;
+                uint32_t w[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) w[j] = Pack16<T>::from_f32(s0f[c * CHUNK + 2 * j], s0f[c * CHUNK + 2 * j + 1]);
+                if (vec_ok && col0 + CHUNK <= p.N) {
+                  uint4* dst = reinterpret_cast<uint4*>(crow + col0);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+                } else {
+                  uint16_t* dst = reinterpret_cast<uint16_t*>(crow + col0);
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) {
+                    if (col0 + 2 * j < p.N) dst[2 * j] = static_cast<uint16_t>(w[j] & 0xFFFFu);
+                    if (col0 + 2 * j + 1 < p.N) dst[2 * j + 1] = static_cast<uint16_t>(w[j] >> 16);
+                  }
+                }
+              }
+            }
+          }
         }
       }
     } else {
@@ -732,13 +861,14 @@ uint32_t* status_address(int dev) {
   return p;
 }
 
-template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR, bool SLABS>
+template <typename T, int BN, int STAGES, int SLEVELS, bool PAIR, bool SLABS, bool NODE32 = false, bool OUT32 = false>
 int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p, int grid,
            cudaStream_t stream, int dev) {
   using C_ = Cfg<BN, STAGES, SLEVELS, PAIR>;
   // set twice at worst when two threads race on a device's first launch: the call is idempotent
   static std::atomic<bool> configured[kMaxDevices];
-  auto kernel = tree_gemm_kernel<T, BN, STAGES, SLEVELS, PAIR, SLABS>;
+  static_assert(!NODE32 || (SLEVELS == 0 && BN <= 128 && !SLABS), "fp32 nodes: the stack lives in tensor memory only");
+  auto kernel = tree_gemm_kernel<T, BN, STAGES, SLEVELS, PAIR, SLABS, NODE32, OUT32>;
   if (dev >= 0 && dev < kMaxDevices && !configured[dev].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(C_::SMEM_BYTES));
@@ -810,6 +940,19 @@ int launch_variant(int tiling, bool deep, const CUtensorMap& ta, const CUtensorM
     case 5: return launch<T, 64, 8, 0, false>(ta, tb, tc, p, grid, stream, dev);
     case 6: return launch<T, 32, 8, 0, false>(ta, tb, tc, p, grid, stream, dev);
     default: return set_error(TBIK_ERR_ARG, "unknown tiling");
+  }
+}
+
+// fp32-node launches: the shallow variants of the 128-, 64- and 32-column tilings (their stack fits tensor memory)
+template <typename T, bool OUT32>
+int launch_node32(int tiling, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
+                  int grid, cudaStream_t stream, int dev) {
+  switch (tiling) {
+    case 1: return launch_one<T, 128, 6, 0, false, false, true, OUT32>(ta, tb, tc, p, grid, stream, dev);
+    case 2: return launch_one<T, 128, 8, 0, true, false, true, OUT32>(ta, tb, tc, p, grid, stream, dev);
+    case 5: return launch_one<T, 64, 8, 0, false, false, true, OUT32>(ta, tb, tc, p, grid, stream, dev);
+    case 6: return launch_one<T, 32, 8, 0, false, false, true, OUT32>(ta, tb, tc, p, grid, stream, dev);
+    default: return set_error(TBIK_ERR_ARG, "fp32 nodes: tiling must be 1, 2, 5 or 6");
   }
 }
 
@@ -981,6 +1124,52 @@ static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int ma
   return best;
 }
 
+// fp32 nodes: a stack level is BN fp32 columns of tensor memory, so a tiling carries (512 - 2 BN) / BN levels above
+// level 0 (2 / 6 / 14 for 128- / 64- / 32-column tiles); no shared-memory or scratch levels, no K-slabs.
+static int node32_levels(int bn) { return (static_cast<int>(TMEM_COLS) - 2 * bn) / bn; }
+
+static Plan plan_node32(int tiling, int M, int N, int L, int max_ctas) {
+  Plan pl{};
+  const Variant& v = kVariants[tiling - 1][0];
+  pl.tiling = tiling;
+  pl.deep = false;
+  pl.splits = 1;
+  pl.slab_levels = L;
+  pl.valid = (tiling == 1 || tiling == 2 || tiling == 5 || tiling == 6) && (L - 1) <= node32_levels(v.bn);
+  const int tile_m = v.pair ? 2 * BM : BM;
+  pl.tiles_m = (M + tile_m - 1) / tile_m;
+  pl.tiles_n = (N + v.bn - 1) / v.bn;
+  int ctas = sm_count(current_device());
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  int units = v.pair ? ctas / 2 : ctas;
+  if (units < 1) units = 1;
+  if (units > pl.tiles_m * pl.tiles_n) units = pl.tiles_m * pl.tiles_n;
+  pl.grid = v.pair ? 2 * units : units;
+  pl.scratch_off = kCounterBytes;
+  return pl;
+}
+
+// The first of the full-rate tilings (256x128 pair, 128x128) that gives (nearly) every SM a tile and can hold the
+// tree; otherwise the tiling that can hold it and occupies the most SMs.
+static Plan auto_plan_node32(int M, int N, int L, int max_ctas) {
+  int ctas = sm_count(current_device());
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  const int enough = ctas - ctas / 5;
+  const int order[4] = {2, 1, 5, 6};
+  Plan best{};
+  int best_ctas = -1;
+  for (int i = 0; i < 4; ++i) {
+    Plan pl = plan_node32(order[i], M, N, L, max_ctas);
+    if (!pl.valid) continue;
+    if (i < 2 && pl.grid >= enough) return pl;
+    if (pl.grid > best_ctas) {
+      best = pl;
+      best_ctas = pl.grid;
+    }
+  }
+  return best;  // .valid is false when no tiling can hold a tree this deep
+}
+
 size_t gemm_workspace_bytes(int M, int N, int64_t K, int leaf) {
   int T, F, L;
   if (M <= 0 || N <= 0 || tree_shape(K, leaf, &T, &F, &L) != TBIK_OK) return 0;
@@ -1010,7 +1199,7 @@ size_t gemm_split_workspace_bytes(int M, int N, int64_t K, int leaf, int tiling,
 // `forced` (optional): a plan chosen by the caller (the entry point with built-in scratch picks one that fits it).
 static int gemm_launch_plan(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw,
                             int64_t ldc, int dtype, int leaf, int T, int F, const Plan& pl, void* workspace,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, int node_dtype = TBIK_NODE_INPUT) {
   const Variant& v = kVariants[pl.tiling - 1][pl.deep ? 1 : 0];
   const int dev = current_device();
 
@@ -1058,11 +1247,17 @@ static int gemm_launch_plan(const void* A, const void* W, void* C, int M, int N,
     p.N = static_cast<int>(ldp);
     p.split_stride = static_cast<int64_t>(M) * ldp;
     p.counters = static_cast<uint32_t*>(workspace);
-  } else if ((reinterpret_cast<uintptr_t>(C) & 15u) == 0 && ldc % 8 == 0 &&
+  } else if (node_dtype == TBIK_NODE_INPUT && (reinterpret_cast<uintptr_t>(C) & 15u) == 0 && ldc % 8 == 0 &&
              make_tmap(&tc, dtype, C, M, N, ldc, BM, true) == TBIK_OK) {
     p.tma_store = 1;
   }
 
+  if (node_dtype == TBIK_NODE_FP32)
+    return dtype == TBIK_DTYPE_BF16 ? launch_node32<__nv_bfloat16, false>(pl.tiling, ta, tb, tc, p, pl.grid, stream, dev)
+                                    : launch_node32<__half, false>(pl.tiling, ta, tb, tc, p, pl.grid, stream, dev);
+  if (node_dtype == TBIK_NODE_FP32_OUT_FP32)
+    return dtype == TBIK_DTYPE_BF16 ? launch_node32<__nv_bfloat16, true>(pl.tiling, ta, tb, tc, p, pl.grid, stream, dev)
+                                    : launch_node32<__half, true>(pl.tiling, ta, tb, tc, p, pl.grid, stream, dev);
   return dtype == TBIK_DTYPE_BF16 ? launch_variant<__nv_bfloat16>(pl.tiling, pl.deep, ta, tb, tc, p, pl.grid, stream, dev)
                                   : launch_variant<__half>(pl.tiling, pl.deep, ta, tb, tc, p, pl.grid, stream, dev);
 }
@@ -1072,8 +1267,8 @@ static int gemm_check_args(const void* A, const void* W, void* C, int M, int N, 
                            int* F, int* L) {
   if (dtype != TBIK_DTYPE_BF16 && dtype != TBIK_DTYPE_FP16)
     return set_error(TBIK_ERR_DTYPE, "tbik_gemm supports bf16 and fp16 operands");
-  if (node_dtype != TBIK_NODE_INPUT)
-    return set_error(TBIK_ERR_DTYPE, "tbik_gemm: only node_dtype = TBIK_NODE_INPUT is implemented");
+  if (node_dtype != TBIK_NODE_INPUT && node_dtype != TBIK_NODE_FP32 && node_dtype != TBIK_NODE_FP32_OUT_FP32)
+    return set_error(TBIK_ERR_DTYPE, "tbik_gemm: node_dtype must be TBIK_NODE_INPUT, TBIK_NODE_FP32 or TBIK_NODE_FP32_OUT_FP32");
   if (M < 0 || N < 0 || K <= 0) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: M, N must be >= 0 and K > 0");
   if (leaf <= 0 || leaf % BK != 0) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: leaf must be a positive multiple of 64");
   if (tiling < 0 || tiling > 6) return set_error(TBIK_ERR_ARG, "tbik_gemm: tiling must be 0..6");
@@ -1085,7 +1280,8 @@ static int gemm_check_args(const void* A, const void* W, void* C, int M, int N, 
   if (lda < K || ldw < K || ldc < N) return set_error(TBIK_ERR_SHAPE, "tbik_gemm: leading dimension smaller than the row");
   if ((reinterpret_cast<uintptr_t>(A) & 15u) || (reinterpret_cast<uintptr_t>(W) & 15u) || (lda % 8) || (ldw % 8))
     return set_error(TBIK_ERR_ALIGN, "tbik_gemm: A and W must be 16-byte aligned with row strides that are multiples of 8 elements");
-  if (reinterpret_cast<uintptr_t>(C) & 1u) return set_error(TBIK_ERR_ALIGN, "tbik_gemm: C must be 2-byte aligned");
+  if (reinterpret_cast<uintptr_t>(C) & (node_dtype == TBIK_NODE_FP32_OUT_FP32 ? 3u : 1u))
+    return set_error(TBIK_ERR_ALIGN, "tbik_gemm: C must be aligned to its element size");
   if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 15u))
     return set_error(TBIK_ERR_ALIGN, "tbik_gemm: workspace must be 16-byte aligned");
   return TBIK_OK;
@@ -1098,6 +1294,20 @@ int gemm_launch(const void* A, const void* W, void* C, int M, int N, int K, int6
   int rc = gemm_check_args(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, tiling, workspace, &T, &F, &L);
   if (rc != TBIK_OK || M == 0 || N == 0) return rc;
   const bool have_ws = workspace != nullptr && ws_bytes > 0;
+
+  if (node_dtype != TBIK_NODE_INPUT) {
+    // fp32 nodes: tensor-memory stack only, one work item per tile
+    if (splits > 1) return set_error(TBIK_ERR_ARG, "tbik_gemm: K-slabs are not available with fp32 nodes");
+    const Plan pl = tiling == 0 ? auto_plan_node32(M, N, L, max_ctas) : plan_node32(tiling, M, N, L, max_ctas);
+    if (!pl.valid) {
+      char msg[200];
+      snprintf(msg, sizeof(msg),
+               "tbik_gemm: with fp32 nodes a tree of %d levels does not fit tensor memory (at most 15 levels; 3 on the "
+               "full-rate tilings): use a wider leaf", L);
+      return set_error(TBIK_ERR_SHAPE, msg);
+    }
+    return gemm_launch_plan(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, T, F, pl, workspace, stream, node_dtype);
+  }
 
   // splits: 0 = automatic (only together with tiling 0), 1 = none, else a power of two of whole subtrees
   if (splits < 0 || splits > kMaxSplits || (splits & (splits - 1)) != 0)
@@ -1157,6 +1367,9 @@ int gemm_launch_static(const void* A, const void* W, void* C, int M, int N, int 
   // In host code `g_static_scratch` is only a handle for the runtime, not a device address: the address
   // the kernel may use has to be asked for, once per device, with that device current.
   static std::atomic<void*> device_addr[kMaxDevices];
+  // fp32 nodes keep their stack in tensor memory: no scratch of any kind, hence nothing to allocate either
+  if (node_dtype == TBIK_NODE_FP32 || node_dtype == TBIK_NODE_FP32_OUT_FP32)
+    return gemm_launch(A, W, C, M, N, K, lda, ldw, ldc, dtype, leaf, node_dtype, 0, 0, nullptr, 0, stream, 0);
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return set_cuda_error(e, "cudaGetDevice");

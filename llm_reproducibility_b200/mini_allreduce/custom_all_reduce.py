@@ -201,6 +201,17 @@ class CustomAllreduce:
             self._native_all_reduce(self._ptr, inp, out, self.buffer_ptrs[self.rank], self.max_size)
         return out
 
+    def all_reduce_rounding(self, view: torch.Tensor, out_dtype: torch.dtype, *, out: torch.Tensor = None) -> torch.Tensor:
+        """Tree all-reduce of fp32 contributions, summed in fp32 and rounded once to `out_dtype` (bf16 / fp16).
+        `view` is a float32 `registered_view` of this object that a producer has filled (addition: the cross-rank
+        levels of a tree whose nodes stay fp32)."""
+        assert view.dtype == torch.float32 and view.is_contiguous()
+        if out is None:
+            out = torch.empty(view.shape, dtype=out_dtype, device=view.device)
+        base = self.buffer_ptrs[self.rank]
+        ops.tree_all_reduce_rounding(self._ptr, base, view.data_ptr() - base, out)
+        return out
+
     def registered_view(self, shape, dtype: torch.dtype) -> Optional[torch.Tensor]:
         """A tensor that aliases the start of this rank's IPC-registered data buffer, or None if it
         does not fit.  A producer (the row-split GEMM) can write its partial result straight into it

@@ -60,6 +60,12 @@ def tree_all_reduce_within(fa: int, reg_base: int, byte_offset: int, out: torch.
     _custom_ar.tree_all_reduce_within(fa, reg_base, byte_offset, out)
 
 
+def tree_all_reduce_rounding(fa: int, reg_base: int, byte_offset: int, out: torch.Tensor) -> None:
+    """Tree all-reduce of fp32 contributions inside a registered buffer, rounded once to `out`'s 16-bit type
+    (addition: the cross-rank levels of a tree whose nodes stay fp32)."""
+    _custom_ar.tree_all_reduce_rounding(fa, reg_base, byte_offset, out)
+
+
 def row_split_layer(fa: int, A: torch.Tensor, B: torch.Tensor, reg_base: int, reg_bytes: int, block_rows: List[int],
                     comm_ctas: int, side_stream: int, leaf: int = 0) -> torch.Tensor:
     """Row-split GEMM + tree all-reduce pipelined over blocks of rows on two streams (addition)."""

@@ -80,7 +80,8 @@ def _pipeline_plan(M: int, N: int, K_local: int, world: int):
     return [first, M - first], _PIPE_COMM_CTAS
 
 
-def tree_matmul_all_reduce(A: torch.Tensor, B: torch.Tensor, device_group=None, leaf=None) -> torch.Tensor:
+def tree_matmul_all_reduce(A: torch.Tensor, B: torch.Tensor, device_group=None, leaf=None,
+                           node_dtype=None) -> torch.Tensor:
     """Row-split layer in one call: this rank's tree matmul, then the tree all-reduce.
 
     Same bits as `tree_all_reduce_sum(matmul_tp_persistent(A, B), group)`.  The GEMM writes its partial
@@ -88,12 +89,29 @@ def tree_matmul_all_reduce(A: torch.Tensor, B: torch.Tensor, device_group=None, 
     all-reduce kernel runs.  Large calls are cut into blocks of rows: block i is reduced on a side stream by a
     few CTAs while the remaining CTAs multiply block i + 1, so most of the NVLink time hides behind the
     tensor-core time (the partial sums of different rows never meet, so the cut cannot change a bit).
-    `leaf` (extension): leaf width, the same on every rank and at every TP degree (see `leaf_for`)."""
+    `leaf` (extension): leaf width, the same on every rank and at every TP degree (see `leaf_for`).
+    `node_dtype=torch.float32` (extension; also TBIK_NODE_FP32=1): the fp32-node mode.  Each rank writes the
+    unrounded fp32 root of its subtree into the registered buffer, the cross-rank levels add in fp32, and the result
+    is rounded once -- bit-identical to `matmul_tp_persistent(A_full, B_full, node_dtype=torch.float32, leaf=leaf)`
+    on one GPU.  `leaf` is then required (`leaf_for_fp32_nodes(K_total, max_tp)`), since only the caller knows the
+    unsharded K."""
     global custom_ar
     from .tree_based_matmul import matmul_tp_persistent
     if custom_ar is None:
         from ..mini_allreduce import CustomTreeAllreduce
         custom_ar = CustomTreeAllreduce(group=device_group, device=A.device, max_size=_max_size())
+    if node_dtype is None and os.environ.get("TBIK_NODE_FP32") == "1":
+        node_dtype = torch.float32
+    if node_dtype == torch.float32:
+        if leaf is None:
+            raise ValueError("fp32 nodes: pass the layer's leaf width (leaf_for_fp32_nodes(K_total, max_tp))")
+        if custom_ar.disabled:
+            raise RuntimeError("fp32 nodes across ranks need the peer-to-peer all-reduce (it is disabled here)")
+        view32 = custom_ar.registered_view((A.shape[0], B.shape[1]), torch.float32)
+        if view32 is None:
+            raise RuntimeError("fp32 nodes: the partial result does not fit the registered buffer (raise TBIK_AR_MAX_SIZE)")
+        matmul_tp_persistent(A, B, out=view32, leaf=leaf, node_dtype=torch.float32, out_dtype=torch.float32)
+        return custom_ar.all_reduce_rounding(view32, A.dtype)
     view = None
     M, N = A.shape[0], B.shape[1]
     if not custom_ar.disabled:

@@ -46,6 +46,35 @@ def leaf_for(K_total: int, max_tp: int = 8, dtype: torch.dtype = torch.bfloat16)
     raise ValueError(f"no leaf width of 256, 128 or 64 splits K = {K_total} into {max_tp} aligned subtrees")
 
 
+def leaf_for_fp32_nodes(K_total: int, max_tp: int = 8) -> int:
+    """Leaf width for the fp32-node mode: K_total / max_tp, so that the tree has exactly `max_tp` leaves, every
+    level is binary, every tensor-parallel degree up to `max_tp` holds a whole subtree per rank, and the stack of
+    the fastest tilings (three levels) suffices.  Long leaves cost no accuracy here: a leaf is one fp32 tensor-core
+    accumulation that is not rounded afterwards."""
+    if max_tp < 1 or max_tp & (max_tp - 1):
+        raise ValueError("max_tp must be a power of two")
+    if K_total % (64 * max_tp) != 0:
+        raise ValueError(f"K = {K_total} does not split into {max_tp} leaves that are multiples of 64")
+    return K_total // max_tp
+
+
+def _node_code(A: torch.Tensor, node_dtype, out_dtype) -> int:
+    """C-ABI node mode for (node_dtype, out_dtype); None / the operand type = the reference's arithmetic."""
+    if node_dtype is None and os.environ.get("TBIK_NODE_FP32") == "1":
+        node_dtype = torch.float32
+    if node_dtype is None or node_dtype == A.dtype:
+        if out_dtype not in (None, A.dtype):
+            raise ValueError("out_dtype other than the operand type needs node_dtype=torch.float32")
+        return _lib.NODE_INPUT
+    if node_dtype != torch.float32:
+        raise ValueError("node_dtype is the operand type or torch.float32")
+    if out_dtype in (None, A.dtype):
+        return _lib.NODE_FP32
+    if out_dtype != torch.float32:
+        raise ValueError("out_dtype is the operand type or torch.float32")
+    return _lib.NODE_FP32_OUT_FP32
+
+
 def _k_major_weight(B: torch.Tensor) -> torch.Tensor:
     """Return W[N,K] (K contiguous) holding B[K,N]'s values.
 
@@ -81,9 +110,14 @@ _WS_NEED = {}  # (device index, M, N, K, leaf) -> bytes of scratch the automatic
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None) or (lambda index: torch.cuda.current_stream(index).cuda_stream)
 
 
-def _launch(A, W, C, M, N, K, leaf, dev, max_ctas=0) -> int:
+def _launch(A, W, C, M, N, K, leaf, dev, max_ctas=0, node=_lib.NODE_INPUT) -> int:
     """Enqueue the GEMM on the current stream of `dev` (which must be the current device)."""
     L = _lib.lib()
+    if node != _lib.NODE_INPUT:
+        # fp32 nodes: the stack lives in tensor memory, no workspace
+        return L.tbik_gemm_ex(A.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K,
+                              max(A.stride(0), K), max(W.stride(0), K), max(C.stride(0), N),
+                              _DTYPE_CODE[A.dtype], leaf, node, max_ctas, 0, None, 0, _raw_stream(dev.index))
     key = (dev.index, M, N, K, leaf)
     need = _WS_NEED.get(key)
     if need is None:
@@ -111,12 +145,17 @@ def prepare_operands(A: torch.Tensor, B: torch.Tensor):
 
 def matmul_tp_persistent(A: torch.Tensor, B: torch.Tensor, bias: Optional[torch.Tensor] = None,
                          *, leaf: Optional[int] = None, out: Optional[torch.Tensor] = None,
-                         max_ctas: int = 0) -> torch.Tensor:
+                         max_ctas: int = 0, node_dtype: Optional[torch.dtype] = None,
+                         out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """C = A @ B with the K reduction in the fixed tree order; returns a new [M, N] tensor of A's dtype.
 
     A: [M, K]; B: [K, N] (any strides; a K-contiguous view such as `weight.t()` is used in place).
     `leaf` (keyword, extension) overrides the leaf width; the default is the reference's 256.
     `max_ctas` (keyword, extension) bounds the CTAs of the launch (0 = one per SM); the bits do not depend on it.
+    `node_dtype=torch.float32` (keyword, extension; also TBIK_NODE_FP32=1): leaves and nodes stay fp32 and only the
+    root is rounded -- the same tree, so the invariances hold, but not the reference's bits; the default leaf is
+    then K / 8 (`leaf_for_fp32_nodes`).  `out_dtype=torch.float32` with it returns the unrounded root (what a
+    tensor-parallel rank contributes to the cross-rank levels).
     """
     assert A.shape[-1] == B.shape[-2], "Dim doesn't match"
     assert A.dim() == 2 and B.dim() == 2
@@ -127,19 +166,24 @@ def matmul_tp_persistent(A: torch.Tensor, B: torch.Tensor, bias: Optional[torch.
     assert B.dtype == A.dtype
     M, K = A.shape
     _, N = B.shape
-    leaf = leaf or int(os.environ.get("TBIK_LEAF", _LEAF[A.dtype]))
+    node = _node_code(A, node_dtype, out_dtype)
+    if node == _lib.NODE_INPUT:
+        leaf = leaf or int(os.environ.get("TBIK_LEAF", _LEAF[A.dtype]))
+    else:
+        leaf = leaf or leaf_for_fp32_nodes(K, 8)
     assert K % leaf == 0
     if A.stride(1) != 1 or A.stride(0) % 8 != 0 or A.data_ptr() % 16 != 0 or (M > 1 and A.stride(0) < K):
         A = A.contiguous()
     W = _k_major_weight(B)
-    C = out if out is not None else torch.empty((M, N), device=A.device, dtype=A.dtype)
-    assert C.shape == (M, N) and C.stride(1) == 1 and C.dtype == A.dtype
+    c_dtype = torch.float32 if node == _lib.NODE_FP32_OUT_FP32 else A.dtype
+    C = out if out is not None else torch.empty((M, N), device=A.device, dtype=c_dtype)
+    assert C.shape == (M, N) and C.stride(1) == 1 and C.dtype == c_dtype
     dev = A.device
     if torch.cuda.current_device() == dev.index:
-        rc = _launch(A, W, C, M, N, K, leaf, dev, max_ctas)
+        rc = _launch(A, W, C, M, N, K, leaf, dev, max_ctas, node)
     else:
         with torch.cuda.device(dev):
-            rc = _launch(A, W, C, M, N, K, leaf, dev, max_ctas)
+            rc = _launch(A, W, C, M, N, K, leaf, dev, max_ctas, node)
     if rc != 0:
         _lib.check(rc, "tbik_gemm_ws")
     if bias is not None:

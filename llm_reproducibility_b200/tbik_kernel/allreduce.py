@@ -147,6 +147,19 @@ def _tree_all_reduce_within(fa: int, reg_base: int, byte_offset: int, out: torch
     _lib.check(rc, "tbik_ar_tree_allreduce_within")
 
 
+def _tree_all_reduce_rounding(fa: int, reg_base: int, byte_offset: int, out: torch.Tensor) -> None:
+    """Tree all-reduce of `out.numel()` fp32 contributions that lie `byte_offset` bytes into the registered buffer
+    at `reg_base`, summed in fp32 and rounded once to `out`'s 16-bit type (tbik_ar_tree_allreduce_rounding)."""
+    if out.dtype not in (torch.bfloat16, torch.float16):
+        raise RuntimeError("the rounded result is bfloat16 or float16")
+    if not _is_weak_contiguous(out):
+        raise RuntimeError("out must be (weakly) contiguous")
+    with torch.cuda.device(out.device):
+        rc = _lib.lib().tbik_ar_tree_allreduce_rounding(fa, reg_base, byte_offset, out.data_ptr(), out.numel(),
+                                                        _DTYPE_CODE[out.dtype], _stream_of(out))
+    _lib.check(rc, "tbik_ar_tree_allreduce_rounding")
+
+
 def _row_split_layer(fa: int, A: torch.Tensor, B: torch.Tensor, reg_base: int, reg_bytes: int, block_rows: List[int],
                      comm_ctas: int, side_stream: int, leaf: int = 0) -> torch.Tensor:
     """out = tree all-reduce over ranks of (A @ B), pipelined over blocks of rows (tbik_ar_row_split_layer).
@@ -219,6 +232,8 @@ def _register() -> None:
     lib.impl("status", _status, any_key)
     lib.define("tree_all_reduce_within(int fa, int reg_base, int byte_offset, Tensor! out) -> ()")
     lib.impl("tree_all_reduce_within", _tree_all_reduce_within, "CUDA")
+    lib.define("tree_all_reduce_rounding(int fa, int reg_base, int byte_offset, Tensor! out) -> ()")
+    lib.impl("tree_all_reduce_rounding", _tree_all_reduce_rounding, "CUDA")
     lib.define("row_split_layer(int fa, Tensor A, Tensor B, int reg_base, int reg_bytes, int[] block_rows, "
                "int comm_ctas, int side_stream, int leaf=0) -> Tensor")
     lib.impl("row_split_layer", _row_split_layer, "CUDA")
@@ -267,6 +282,10 @@ def meta_size(*args, **kwargs):
 
 def tree_all_reduce_within(*args, **kwargs):
     return torch.ops.tbik_kernel.tree_all_reduce_within.default(*args, **kwargs)
+
+
+def tree_all_reduce_rounding(*args, **kwargs):
+    return torch.ops.tbik_kernel.tree_all_reduce_rounding.default(*args, **kwargs)
 
 
 def row_split_layer(*args, **kwargs):

@@ -344,3 +344,72 @@ def pipelined_layer(rank, world):
     dist.barrier()
     tar.reset_communicator()
     return True
+
+
+def fp32_nodes_layer(rank, world):
+    """fp32-node mode across ranks: every rank's unrounded subtree root goes into the registered buffer, the
+    rounding all-reduce adds the roots in fp32 in rank-pair tree order and rounds once.  Checked against the
+    unsharded single-device call (bit for bit), against the CPU oracle on operands with exact leaves, and -- the
+    all-reduce alone, both schedules -- against the same tree written with torch adds."""
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from oracle.tbik_ref import tbik_matmul_ref
+    from llm_reproducibility_b200.mini_allreduce import custom_all_reduce_ops as ops
+    from llm_reproducibility_b200.tbik import tree_based_all_reduce as tar
+    from llm_reproducibility_b200.tbik.tree_based_matmul import leaf_for_fp32_nodes, matmul_tp_persistent
+
+    device = torch.device(f"cuda:{rank}")
+    g = torch.Generator(device=device).manual_seed(977)
+    for dtype, (M, K, N) in ((torch.bfloat16, (1024, 4096, 4096)), (torch.bfloat16, (300, 12288, 1024)),
+                             (torch.float16, (64, 4096, 512)), (torch.bfloat16, (4096, 4096, 4096))):
+        leaf = leaf_for_fp32_nodes(K, 8)
+        X = torch.randn(M, K, generator=g, device=device).to(dtype)
+        W = (torch.randn(N, K, generator=g, device=device) * 0.02).to(dtype)
+        ks = K // world
+        want = matmul_tp_persistent(X, W.t(), leaf=leaf, node_dtype=torch.float32)
+        for _ in range(2):
+            got = tar.tree_matmul_all_reduce(X[:, rank * ks:(rank + 1) * ks], W[:, rank * ks:(rank + 1) * ks].t(), None,
+                                             leaf=leaf, node_dtype=torch.float32)
+        torch.cuda.synchronize()
+        tar.custom_ar.check_status()
+        assert got.dtype == dtype
+        assert torch.equal(bits(got), bits(want)), (dtype, M, K, N)
+    # operands with exact leaves and inexact node sums: the CPU oracle's fp32-node tree
+    M, K, N, leaf = 128, 4096, 256, 512
+    cg = torch.Generator().manual_seed(5)
+    A = torch.randint(-15, 16, (M, K), generator=cg).float()
+    B = torch.randint(-15, 16, (K, N), generator=cg).float()
+    for i in range(K // leaf):
+        A[:, i * leaf:(i + 1) * leaf] *= 2.0 ** (-5 * i)
+    A, B = A.to(torch.bfloat16), B.to(torch.bfloat16)
+    want = tbik_matmul_ref(A, B, leaf, torch.float32, torch.bfloat16)
+    ks = K // world
+    got = tar.tree_matmul_all_reduce(A[:, rank * ks:(rank + 1) * ks].to(device), B[rank * ks:(rank + 1) * ks].to(device),
+                                     None, leaf=leaf, node_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert torch.equal(bits(got.cpu()), bits(want))
+
+    # the rounding all-reduce alone, one-shot and two-shot, ragged part sizes
+    ar = tar.custom_ar
+    for numel, seed in ((8 * 1237, 61), (1 << 16, 62), (8 * 100003, 63), (1 << 22, 64)):
+        xs = [t.float() * 1.37 for t in _inputs(world, numel, torch.bfloat16, seed, device)]
+        parts = [x.clone() for x in xs]
+        stride = 1
+        while stride < world:
+            for i in range(0, world, 2 * stride):
+                parts[i] = parts[i] + parts[i + stride]
+            stride *= 2
+        for out_dtype in (torch.bfloat16, torch.float16):
+            want = parts[0].to(out_dtype)
+            for one_max in (1 << 30, 1024):   # everything one-shot / everything two-shot
+                ops.configure(ar._ptr, ops.CFG_ONESHOT_MAX_BYTES, one_max)
+                view = ar.registered_view((numel,), torch.float32)
+                view.copy_(xs[rank])
+                got = ar.all_reduce_rounding(view, out_dtype)
+                torch.cuda.synchronize()
+                ar.check_status()
+                assert torch.equal(bits(got), bits(want)), (numel, out_dtype, one_max)
+    ops.configure(ar._ptr, ops.CFG_ONESHOT_MAX_BYTES, 0)
+    dist.barrier()
+    tar.reset_communicator()
+    return True

@@ -54,6 +54,11 @@ def test_pipelined_row_blocks_match_single_device():
 
 
 @needs_multi
+def test_fp32_node_layer_matches_single_device_and_oracle():
+    assert all(run_ranks(w.fp32_nodes_layer, _world(), backend="nccl"))
+
+
+@needs_multi
 def test_a_wait_that_runs_out_returns_and_reports():
     """No GPU hangs or faults here: the lonely kernel's bounded wait (20 ms) expires, it writes a status record
     and returns; the peers are idle on the host meanwhile."""
