@@ -606,8 +606,9 @@ static int ar_run_impl(tbik_ar_t h, const void* inp, void* out, int64_t numel, i
   // more ranks: measured on 8 GPUs, one-shot wins up to 1 MiB (26 vs 37 us at 512 KiB, 32 vs 38 us at 1 MiB), loses from 2 MiB
   if (one_max == 0) one_max = c->world <= 2 ? ~size_t(0) : (1u << 20);
   // rounding variant on two ranks: the two-shot schedule pulls 3/4 of the one-shot's bytes (half the fp32
-  // contributions, then half the 16-bit result), which pays for its second barrier on long messages only
-  if (cast && c->oneshot_max_bytes == 0 && c->world == 2) one_max = 32u << 20;
+  // contributions, then half the 16-bit result), which pays for its second barrier from 16 MiB of contributions on
+  // (measured on 2 GPUs, one-shot / two-shot: 25.2 / 25.8 us at 4 MiB, 44.5 / 43.1 at 16, 121.7 / 97.9 at 64)
+  if (cast && c->oneshot_max_bytes == 0 && c->world == 2) one_max = 8u << 20;
   bool twoshot = c->world > 1 && bytes > one_max && c->full_nvlink;
   if (twoshot) {
     // the last rank's part of the result in 16-byte packs, rounded up (rounding variant: 8 elements per pack)

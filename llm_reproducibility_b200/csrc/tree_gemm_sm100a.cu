@@ -44,6 +44,14 @@
 
 namespace tbik {
 
+// Development aid, off in the shipped library.  Built with -DTBIK_WAIT_PROFILE=1 block 0's UMMA issuer counts the SM
+// cycles it waits for a drained accumulator and for a landed pipeline stage; with =2 its first epilogue warp counts
+// the cycles it waits for a finished leaf and the cycles from there to releasing the accumulator.  The two counts
+// come back as words 1 and 2 of tbik_gemm_status (word 3 is block 0's total, word 0 stays the error code).
+#ifndef TBIK_WAIT_PROFILE
+#define TBIK_WAIT_PROFILE 0
+#endif
+
 constexpr int BM = 128;   // rows of C per CTA
 constexpr int BK = 64;    // one 128-byte swizzle row of 16-bit elements
 constexpr int UMMA_K = 16;
@@ -97,7 +105,11 @@ struct Cfg {
   static constexpr uint32_t TMEM_STACK_COL0 = 2 * BN;
   // shared memory map (offsets from a 1024-byte aligned base)
   static constexpr uint32_t OFF_STACK = STAGES * STAGE_BYTES;
-  static constexpr uint32_t OFF_FULL = OFF_STACK + SLEVELS * LEVEL_WORDS * 4;
+  // Variants without stack levels in shared memory get a buffer of their own for staging the finished tile of C
+  // (for the TMA stores) when it fits beside the pipeline; the others stage in the slot of stack level 1.
+  static constexpr uint32_t STAGING_BYTES =
+      (SLEVELS == 0 && BN >= 128 && STAGES * STAGE_BYTES + BM * BN * 2 + 2048 <= 232448) ? BM * BN * 2 : 0;
+  static constexpr uint32_t OFF_FULL = OFF_STACK + (SLEVELS > 0 ? SLEVELS * LEVEL_WORDS * 4 : STAGING_BYTES);
   static constexpr uint32_t OFF_EMPTY = OFF_FULL + 8 * STAGES;
   static constexpr uint32_t OFF_TFULL = OFF_EMPTY + 8 * STAGES;
   static constexpr uint32_t OFF_TEMPTY = OFF_TFULL + 16;
@@ -315,6 +327,9 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       uint32_t leaf_ctr = 0;
       bool ok = true;
+#if TBIK_WAIT_PROFILE == 1
+      long long w_acc = 0, w_stage = 0;  // cycles block 0's issuer waited for a drained accumulator / a landed stage
+#endif
       // completion signal to this CTA's barrier and, for a pair, to the partner's twin barrier
       auto commit = [&](uint32_t bar) {
         if constexpr (PAIR) {
@@ -328,20 +343,32 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int leaf = 0; ok && leaf < p.T; ++leaf, ++leaf_ctr) {
           const uint32_t a = leaf_ctr & 1u;
           const uint32_t aphase = (leaf_ctr >> 1) & 1u;
+#if TBIK_WAIT_PROFILE == 1
+          const long long t_acc = clock64();
+#endif
           if (!mbar_wait_bounded(tempty_bar(a), aphase ^ 1u, abort_flag, WAIT_LIMIT_NS)) {
             ok = false;
             role_failed = 2;
             break;
           }
+#if TBIK_WAIT_PROFILE == 1
+          w_acc += clock64() - t_acc;
+#endif
           tc_fence_after_sync();
           const uint32_t tmem_d = tmem_base + a * BN;
           // one 64-wide k-block: wait for its stage, four UMMAs, release the stage
           auto kblock = [&](int kb) -> bool {
+#if TBIK_WAIT_PROFILE == 1
+            const long long t_stage = clock64();
+#endif
             if (!mbar_wait_bounded(full_bar(stage), phase, abort_flag, WAIT_LIMIT_NS)) {
               ok = false;
               role_failed = 3;
               return false;
             }
+#if TBIK_WAIT_PROFILE == 1
+            w_stage += clock64() - t_stage;
+#endif
             tc_fence_after_sync();
             const uint64_t sd = static_cast<uint64_t>(stage) * (STAGE_BYTES >> 4);
 #pragma unroll
@@ -381,6 +408,12 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (ok) commit(tfull_bar(a));
         }
       }
+#if TBIK_WAIT_PROFILE == 1
+      if (blockIdx.x == 0 && p.status != nullptr) {
+        p.status[1] = static_cast<uint32_t>(w_acc);
+        p.status[2] = static_cast<uint32_t>(w_stage);
+      }
+#endif
     }
   } else if (warp >= EPI_WARP0) {
     // ------------------------------------------------------------ epilogue: drain + tree combine
@@ -443,10 +476,12 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     };
 
-    // C leaves through the TMA unit when possible: the finished tile is staged (128-byte swizzle) in the
-    // shared-memory slot of stack level 1, which is free once the tree is complete, and one thread issues
-    // one tiled store per 64 columns.  The slot may only be rewritten after those stores have read it.
-    const bool tma_c = SLEVELS > 0 && p.tma_store != 0;
+    // C leaves through the TMA unit when possible: the finished tile is staged (128-byte swizzle) in shared memory
+    // -- in a buffer of its own, or in the slot of stack level 1, which is free once the tree is complete -- and one
+    // thread issues one tiled store per 64 columns.  The buffer may only be rewritten after those stores have read
+    // it.  (Storing the root from registers instead costs a 256x128 tile about 2200 cycles, a tenth of its time at
+    // K = 4096: every store instruction of a warp touches 32 rows of C.)
+    const bool tma_c = (SLEVELS > 0 || C_::STAGING_BYTES > 0) && p.tma_store != 0;
     bool staging_busy = false;
     bool ok = true;
     uint32_t epi_phase = 0;
@@ -613,6 +648,10 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else {
     uint32_t s0[NW];  // the open level-0 group; once it closes, the node that climbs the tree
     uint32_t leaf_ctr = 0;
+#if TBIK_WAIT_PROFILE >= 2
+    long long w_full = 0, w_drain = 0;  // cycles this warp waited for a finished leaf / spent until it released it
+    long long t_rel = 0;
+#endif
     for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
       int tm, tn;
       tile_coords(p, tile / p.splits, tm, tn);
@@ -623,11 +662,21 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int leaf = 0; ok && leaf < p.T; ++leaf, ++leaf_ctr) {
         const uint32_t a = leaf_ctr & 1u;
         const uint32_t aphase = (leaf_ctr >> 1) & 1u;
+#if TBIK_WAIT_PROFILE == 2
+        const long long t_full = clock64();
+#endif
+#if TBIK_WAIT_PROFILE == 4
+        const long long t_leaf0 = clock64();
+#endif
         if (!mbar_wait_bounded(tfull_bar(a), aphase, abort_flag, WAIT_LIMIT_NS)) {
           ok = false;
           role_failed = 4;
           break;
         }
+#if TBIK_WAIT_PROFILE == 2
+        const long long t_got = clock64();
+        w_full += t_got - t_full;
+#endif
         tc_fence_after_sync();
         if constexpr (C_::TMEM_LEVELS > 0) tmem_wait_st();  // stack stores of earlier leaves have landed
         const uint32_t tacc = tmem_base + lane_off + a * BN + h * C_::COLS_PER_WARP;
@@ -645,6 +694,12 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               tc_fence_before_sync();
               __syncwarp();
               if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * a);  // accumulator may be overwritten now
+#if TBIK_WAIT_PROFILE == 2
+              w_drain += clock64() - t_got;
+#endif
+#if TBIK_WAIT_PROFILE == 3
+              t_rel = clock64();
+#endif
             }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -653,6 +708,10 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
         }
+#if TBIK_WAIT_PROFILE == 3
+        const long long t_conv = clock64();
+        w_full += t_conv - t_rel;  // converting and adding the last chunk after the release
+#endif
         if (++c0 < p.F) continue;
         c0 = 0;
         // levels >= 1: binary counter over finished groups
@@ -666,14 +725,27 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           gb >>= 1;
           ++lvl;
         }
+#if TBIK_WAIT_PROFILE == 3
+        w_drain += clock64() - t_conv;  // the loads and adds of the climb
+#endif
+#if TBIK_WAIT_PROFILE == 4
+        const long long t_store0 = clock64();
+        w_full += t_store0 - t_leaf0;  // whole leaves that closed a group, up to the store
+#endif
         if (lvl < p.L) {
           if (lvl - 1 == C_::TMEM_LEVELS) staging_release();  // about to overwrite the staging slot
           stack_store(lvl, s0);
+#if TBIK_WAIT_PROFILE == 4
+          w_drain += clock64() - t_store0;  // stack stores
+#endif
         } else if (tma_c) {
+#if TBIK_WAIT_PROFILE == 5
+          const long long t_root0 = clock64();
+#endif
           staging_release();
           // the slot is laid out per thread as a stack level but per row as a staged tile: nobody may
           // write tile rows into it before every warp has popped its own level-1 words
-          epi_sync();
+          if constexpr (SLEVELS > 0) epi_sync();
           constexpr int CCH = C_::COLS_PER_WARP / 64;  // 64-column boxes per warp
           const int r = q * 32 + lane;
 #pragma unroll
@@ -694,7 +766,13 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             bulk_commit_group();
           }
           staging_busy = true;
+#if TBIK_WAIT_PROFILE == 5
+          w_full += clock64() - t_root0;  // staged root store
+#endif
         } else {
+#if TBIK_WAIT_PROFILE == 5
+          const long long t_root0 = clock64();
+#endif
           if (row < p.M) {
           // root of the tile's tree: write this thread's BN/2 columns of C
 #pragma unroll
@@ -716,6 +794,9 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
           }
+#if TBIK_WAIT_PROFILE == 5
+          w_drain += clock64() - t_root0;  // direct root store
+#endif
           if (SLABS && p.splits > 1) {
             // K-slabs: this was one of the tile's `splits` subtree roots.  Count the arrival; the CTA that brings
             // the last root adds all of them in the fixed pairwise order and writes C.  Which CTA that is depends
@@ -745,6 +826,12 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
     }
+#if TBIK_WAIT_PROFILE >= 2
+    if (blockIdx.x == 0 && warp == EPI_WARP0 && lane == 0 && p.status != nullptr) {
+      p.status[1] = static_cast<uint32_t>(w_full);
+      p.status[2] = static_cast<uint32_t>(w_drain);
+    }
+#endif
     }  // draining warps
   }
 
