@@ -456,6 +456,16 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
     };
+    // Tensor-memory levels only: ask for level `lvl` without waiting (the caller waits with tmem_wait_ld()).
+    auto stack_issue = [&](int lvl, uint32_t (&t)[NW]) {
+      const uint32_t col = tmem_base + lane_off + C_::TMEM_STACK_COL0 + (lvl - 1) * (BN / 2) + h * (C_::COLS_PER_WARP / 2);
+      if constexpr (NW == 16) {
+        tmem_ld16(col, *reinterpret_cast<uint32_t(*)[16]>(&t[0]));
+      } else {
+#pragma unroll
+        for (int w = 0; w < NW / 32; ++w) tmem_ld32(col + w * 32, *reinterpret_cast<uint32_t(*)[32]>(&t[w * 32]));
+      }
+    };
     auto stack_store = [&](int lvl, const uint32_t (&v)[NW]) {
       const int idx = lvl - 1;
       if (idx < C_::TMEM_LEVELS) {
@@ -647,6 +657,8 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     } else {
     uint32_t s0[NW];  // the open level-0 group; once it closes, the node that climbs the tree
+    constexpr bool PREFETCH1 = C_::TMEM_LEVELS >= 1 && NW <= 32;
+    uint32_t pre1[PREFETCH1 ? NW : 1];  // stack level 1, requested ahead of the drain
     uint32_t leaf_ctr = 0;
 #if TBIK_WAIT_PROFILE >= 2
     long long w_full = 0, w_drain = 0;  // cycles this warp waited for a finished leaf / spent until it released it
@@ -662,6 +674,16 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int leaf = 0; ok && leaf < p.T; ++leaf, ++leaf_ctr) {
         const uint32_t a = leaf_ctr & 1u;
         const uint32_t aphase = (leaf_ctr >> 1) & 1u;
+        // A leaf that closes an odd-numbered group meets stack level 1 right after its drain: ask tensor memory for
+        // it now, while the leaf is still being multiplied, so that the climb starts with the operand at hand.
+        bool have1 = false;
+        if constexpr (PREFETCH1) {
+          if (c0 + 1 == p.F && (g & 1u) && p.L > 1) {
+            tmem_wait_st();  // the store that filled level 1 has landed
+            stack_issue(1, pre1);
+            have1 = true;
+          }
+        }
 #if TBIK_WAIT_PROFILE == 2
         const long long t_full = clock64();
 #endif
@@ -685,12 +707,13 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           // drain the accumulator chunk by chunk; the next chunk flies while this one is rounded and added
           uint32_t raw[2][32];
           tmem_ld32(tacc, raw[0]);
+          if constexpr (NCH == 2) tmem_ld32(tacc + CHUNK, raw[1]);  // two chunks: both in flight, one wait, release
 #pragma unroll
           for (int c = 0; c < NCH; ++c) {
-            tmem_wait_ld();
-            if (c + 1 < NCH) {
+            if (NCH != 2 || c == 0) tmem_wait_ld();
+            if (NCH != 2 && c + 1 < NCH) {
               tmem_ld32(tacc + (c + 1) * CHUNK, raw[(c + 1) & 1]);
-            } else {
+            } else if (NCH == 2 ? c == 0 : true) {
               tc_fence_before_sync();
               __syncwarp();
               if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * a);  // accumulator may be overwritten now
@@ -717,6 +740,14 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // levels >= 1: binary counter over finished groups
         uint32_t gb = g++;
         int lvl = 1;
+        if constexpr (PREFETCH1) {
+          if (have1) {  // arrived with the drain's wait
+#pragma unroll
+            for (int w = 0; w < NW; ++w) s0[w] = Pack16<T>::add(pre1[w], s0[w]);
+            gb >>= 1;
+            lvl = 2;
+          }
+        }
         while (lvl < p.L && (gb & 1u)) {
           uint32_t t[NW];
           stack_load(lvl, t);
