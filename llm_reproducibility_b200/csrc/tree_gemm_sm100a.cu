@@ -517,6 +517,35 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     };
 
+    // The finished tile of C (this thread's NW packed words of its row) to shared memory, then out with TMA stores.
+    // Every epilogue thread calls it, also those whose row lies beyond M: the stores clip.
+    auto stage_root = [&](const uint32_t (&v)[NW], int tm, int tn) {
+      staging_release();
+      // a stack slot is laid out per thread as a stack level but per row as a staged tile: nobody may
+      // write tile rows into it before every warp has popped its own level-1 words
+      if constexpr (SLEVELS > 0) epi_sync();
+      constexpr int CCH = C_::COLS_PER_WARP / 64;  // 64-column boxes per warp
+      const int r = q * 32 + lane;
+#pragma unroll
+      for (int cc = 0; cc < CCH; ++cc) {
+        uint8_t* box = reinterpret_cast<uint8_t*>(smem_stack) + (h * CCH + cc) * (BM * 128) + r * 128;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          *reinterpret_cast<uint4*>(box + ((u ^ (r & 7)) << 4)) =
+              make_uint4(v[cc * 32 + 4 * u], v[cc * 32 + 4 * u + 1], v[cc * 32 + 4 * u + 2], v[cc * 32 + 4 * u + 3]);
+      }
+      fence_proxy_async_smem();
+      epi_sync();
+      if (ok && epi_tid == 0) {
+        const uint32_t sbase = smem_base + C_::OFF_STACK;
+        const int row0 = tm * TILE_M + static_cast<int>(cta_rank) * BM;
+#pragma unroll
+        for (int b = 0; b < BN / 64; ++b) tma_store_2d(&tmap_c, sbase + b * (BM * 128), tn * BN + b * 64, row0);
+        bulk_commit_group();
+      }
+      staging_busy = true;
+    };
+
     if (h >= C_::EPI_HALVES) {
       // narrow tiles: this warp has no columns to drain; it only keeps the accumulator hand-shake going
       uint32_t ctr = 0;
@@ -607,6 +636,12 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               for (int j = 0; j < CHUNK; ++j) t[j] = __float_as_uint(s0f[c * CHUNK + j]);
               tmem_st32(stack_col(lvl, c), t);
             }
+          } else if (!OUT32 && tma_c) {
+            // the one rounding of this mode, then out through the staging buffer
+            uint32_t w[NW];
+#pragma unroll
+            for (int j = 0; j < NW; ++j) w[j] = Pack16<T>::from_f32(s0f[2 * j], s0f[2 * j + 1]);
+            stage_root(w, tm, tn);
           } else if (row < p.M) {
             // root of the tile's tree
             if constexpr (OUT32) {
@@ -773,30 +808,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #if TBIK_WAIT_PROFILE == 5
           const long long t_root0 = clock64();
 #endif
-          staging_release();
-          // the slot is laid out per thread as a stack level but per row as a staged tile: nobody may
-          // write tile rows into it before every warp has popped its own level-1 words
-          if constexpr (SLEVELS > 0) epi_sync();
-          constexpr int CCH = C_::COLS_PER_WARP / 64;  // 64-column boxes per warp
-          const int r = q * 32 + lane;
-#pragma unroll
-          for (int cc = 0; cc < CCH; ++cc) {
-            uint8_t* box = reinterpret_cast<uint8_t*>(smem_stack) + (h * CCH + cc) * (BM * 128) + r * 128;
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-              *reinterpret_cast<uint4*>(box + ((u ^ (r & 7)) << 4)) =
-                  make_uint4(s0[cc * 32 + 4 * u], s0[cc * 32 + 4 * u + 1], s0[cc * 32 + 4 * u + 2], s0[cc * 32 + 4 * u + 3]);
-          }
-          fence_proxy_async_smem();
-          epi_sync();
-          if (ok && epi_tid == 0) {
-            const uint32_t sbase = smem_base + C_::OFF_STACK;
-            const int row0 = tm * TILE_M + static_cast<int>(cta_rank) * BM;
-#pragma unroll
-            for (int b = 0; b < BN / 64; ++b) tma_store_2d(&tmap_c, sbase + b * (BM * 128), tn * BN + b * 64, row0);
-            bulk_commit_group();
-          }
-          staging_busy = true;
+          stage_root(s0, tm, tn);
 #if TBIK_WAIT_PROFILE == 5
           w_full += clock64() - t_root0;  // staged root store
 #endif
@@ -1365,7 +1377,7 @@ static int gemm_launch_plan(const void* A, const void* W, void* C, int M, int N,
     p.N = static_cast<int>(ldp);
     p.split_stride = static_cast<int64_t>(M) * ldp;
     p.counters = static_cast<uint32_t*>(workspace);
-  } else if (node_dtype == TBIK_NODE_INPUT && (reinterpret_cast<uintptr_t>(C) & 15u) == 0 && ldc % 8 == 0 &&
+  } else if (node_dtype != TBIK_NODE_FP32_OUT_FP32 && (reinterpret_cast<uintptr_t>(C) & 15u) == 0 && ldc % 8 == 0 &&
              make_tmap(&tc, dtype, C, M, N, ldc, BM, true) == TBIK_OK) {
     p.tma_store = 1;
   }
