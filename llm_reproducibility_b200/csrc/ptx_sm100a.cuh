@@ -120,6 +120,28 @@ TBIK_DEVICE void tma_load_2d(uint32_t smem_dst, const void* tmap, int32_t x, int
 }
 
 
+// L2 eviction priorities for loads: 0 = normal, 1 = evict first (streamed once), 2 = evict last (worth keeping).
+TBIK_DEVICE uint64_t l2_policy(int kind) {
+  uint64_t pol;
+  if (kind == 1) {
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  } else if (kind == 2) {
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  } else {
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
+  }
+  return pol;
+}
+
+// The same tiled load with an L2 eviction priority attached.
+TBIK_DEVICE void tma_load_2d_hint(uint32_t smem_dst, const void* tmap, int32_t x, int32_t y, uint32_t bar,
+                                  uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
+
 // Tiled store shared memory -> global through the TMA unit (bulk async-group completion).
 TBIK_DEVICE void tma_store_2d(const void* tmap, uint32_t smem_src, int32_t x, int32_t y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"

@@ -32,6 +32,7 @@
 //                   128 rows of A and half of the W tile and drains its own half of the accumulator;
 //                   the partner CTA tells the leader's UMMA issuer when its half of a stage landed.
 #include <cuda.h>
+#include <cstdlib>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -87,6 +88,10 @@ struct GemmParams {
   // rows: the rest of the 128-row shared-memory tile keeps whatever it held, the UMMA multiplies that too, and
   // the rows of C it produces are never stored (a row of C depends on no other row of A).
   uint32_t a_box_bytes;
+  // L2 eviction priority of the loads of A and of W (0 normal, 1 evict first, 2 evict last).  Within a group of row
+  // tiles every wave of CTAs re-reads the group's rows of A and meets new rows of W; at K = 12288 one wave touches
+  // about 79 MB, so under plain LRU a line of A has left L2 by the time the next wave asks for it.
+  int hint_a, hint_b;
   uint32_t* status;      // [0] error code, [1] block, [2] role, [3] SM cycles of block 0 (last launch)
 };
 
@@ -250,6 +255,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t phase = 0;
       const int kblocks = p.T * p.kblocks_per_leaf;
       bool ok = true;
+      const uint64_t pol_a = l2_policy(p.hint_a), pol_b = l2_policy(p.hint_b);
       for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
         int tm, tn;
         tile_coords(p, tile / p.splits, tm, tn);
@@ -266,8 +272,8 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           // every CTA tracks its own bytes on its own barrier
           mbar_arrive_expect_tx(full_bar(stage), p.a_box_bytes + C_::B_STAGE_BYTES);
-          tma_load_2d(sa, &tmap_a, (kb0 + kb) * BK, row0, full_bar(stage));
-          tma_load_2d(sa + A_STAGE_BYTES, &tmap_b, (kb0 + kb) * BK, wrow0, full_bar(stage));
+          tma_load_2d_hint(sa, &tmap_a, (kb0 + kb) * BK, row0, full_bar(stage), pol_a);
+          tma_load_2d_hint(sa + A_STAGE_BYTES, &tmap_b, (kb0 + kb) * BK, wrow0, full_bar(stage), pol_b);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -1357,6 +1363,23 @@ static int gemm_launch_plan(const void* A, const void* W, void* C, int M, int N,
   p.tiles_m = pl.tiles_m;
   p.tiles_n = pl.tiles_n;
   p.group_m = v.pair ? 8 : 16;  // 2048 rows of A per group: a wave of CTAs covers a near-square block of C
+  {
+    // More rows than one group: ask L2 to keep the rows of A (evict last), which every wave of the group reads
+    // again; W keeps the normal priority.  Measured at M = 8192 (o_proj / down_proj, TFLOP/s, burst and 1.5 s back
+    // to back on one GPU): no hints 1250 / 1157 and 1038 / 996; A last + W normal 1263 / 1186 and 1063 / 1028; A last
+    // + W first 1223 / 1151 and 1019 / 986; W first alone 1189 / 1128 and 992 / 969.
+    // TBIK_GEMM_L2_HINTS = "ab" (two digits 0..2, for A and W) overrides the choice, for measurements.
+    static const int forced = [] {
+      const char* e = getenv("TBIK_GEMM_L2_HINTS");
+      return (e && e[0] >= '0' && e[0] <= '2' && e[1] >= '0' && e[1] <= '2') ? (e[0] - '0') * 3 + (e[1] - '0') : -1;
+    }();
+    p.hint_a = M > 2048 ? 2 : 0;
+    p.hint_b = 0;
+    if (forced >= 0) {
+      p.hint_a = forced / 3;
+      p.hint_b = forced % 3;
+    }
+  }
   p.scratch = workspace ? reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(workspace) + pl.scratch_off) : nullptr;
   p.scratch_levels = pl.scratch_levels;
   p.status = status_address(dev);
