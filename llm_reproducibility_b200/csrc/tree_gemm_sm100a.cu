@@ -703,7 +703,7 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t leaf_ctr = 0;
 #if TBIK_WAIT_PROFILE >= 2
     long long w_full = 0, w_drain = 0;  // cycles this warp waited for a finished leaf / spent until it released it
-    long long t_rel = 0;
+    [[maybe_unused]] long long t_rel = 0;
 #endif
     for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
       int tm, tn;
