@@ -120,6 +120,12 @@ TBIK_DEVICE void tma_load_2d(uint32_t smem_dst, const void* tmap, int32_t x, int
 }
 
 
+// Register budget of the calling warpgroup (all four warps of it must execute the same instruction).
+template <int N>
+TBIK_DEVICE void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+TBIK_DEVICE void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
 // L2 eviction priorities for loads: 0 = normal, 1 = evict first (streamed once), 2 = evict last (worth keeping).
 TBIK_DEVICE uint64_t l2_policy(int kind) {
   uint64_t pol;

@@ -246,6 +246,13 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   int role_failed = 0;  // which role observed the abort (for the status word)
   const long long cycles0 = clock64();
 
+  // The 256x256 pair tile with nodes of the operand type: its accumulators fill tensor memory, so the epilogue keeps
+  // TWO level-0 groups in registers (stack level 1 never leaves them) and needs more registers than a 384-thread
+  // launch hands out evenly: the producer / issuer warpgroup gives up what it does not use.
+  constexpr bool TWOGROUP = BN == 256 && PAIR && !SLABS && !NODE32;
+
+  if (warp < EPI_WARP0) {
+  if constexpr (TWOGROUP) setmaxnreg_dec<56>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (every CTA)
     // elect.sync, not lane == 0: the compiler then knows that one thread runs the branch and feeds the TMA
@@ -421,8 +428,10 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
 #endif
     }
-  } else if (warp >= EPI_WARP0) {
+  }
+  } else {
     // ------------------------------------------------------------ epilogue: drain + tree combine
+    if constexpr (TWOGROUP) setmaxnreg_inc<224>();
     const int q = warp & 3;                 // TMEM lane quadrant this warp may access
     const int h = (warp - EPI_WARP0) >> 2;  // which half of the accumulator's columns
     const uint32_t lane_off = static_cast<uint32_t>(q * 32) << 16;
@@ -690,6 +699,97 @@ tree_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     if (col0 + 2 * j < p.N) dst[2 * j] = static_cast<uint16_t>(w[j] & 0xFFFFu);
                     if (col0 + 2 * j + 1 < p.N) dst[2 * j + 1] = static_cast<uint16_t>(w[j] >> 16);
                   }
+                }
+              }
+            }
+          }
+        }
+      }
+    } else if constexpr (TWOGROUP) {
+      // ---------------------------------------------------------- two level-0 groups per trip, level 1 in registers
+      // Stack level lvl >= 2 lives in slot lvl - 2: the shared-memory slot first, the scratch after it.
+      uint32_t sA[NW], s0[NW];
+      uint32_t leaf_ctr = 0;
+      // wait for the next leaf and drain it into dst (add0: onto what dst holds -- level 0, radix F, left to right)
+      auto drain_leaf = [&](uint32_t (&dst)[NW], bool add0) -> bool {
+        const uint32_t a = leaf_ctr & 1u;
+        const uint32_t aphase = (leaf_ctr >> 1) & 1u;
+        ++leaf_ctr;
+        if (!mbar_wait_bounded(tfull_bar(a), aphase, abort_flag, WAIT_LIMIT_NS)) {
+          ok = false;
+          role_failed = 4;
+          return false;
+        }
+        tc_fence_after_sync();
+        const uint32_t tacc = tmem_base + lane_off + a * BN + h * C_::COLS_PER_WARP;
+        uint32_t raw[2][32];
+        tmem_ld32(tacc, raw[0]);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          tmem_wait_ld();
+          if (c + 1 < NCH) {
+            tmem_ld32(tacc + (c + 1) * CHUNK, raw[(c + 1) & 1]);
+          } else {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * a);  // accumulator may be overwritten now
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const uint32_t v = Pack16<T>::from_f32(__uint_as_float(raw[c & 1][2 * j]), __uint_as_float(raw[c & 1][2 * j + 1]));
+            dst[c * 16 + j] = add0 ? Pack16<T>::add(dst[c * 16 + j], v) : v;
+          }
+        }
+        return true;
+      };
+      for (int tile = unit; ok && tile < num_tiles; tile += num_units) {
+        int tm, tn;
+        tile_coords(p, tile, tm, tn);
+        const int row = tm * TILE_M + static_cast<int>(cta_rank) * BM + q * 32 + lane;
+        T* crow = reinterpret_cast<T*>(p.C) + static_cast<int64_t>(row) * p.ldc;
+        const int supers = p.L >= 2 ? (p.T / p.F) >> 1 : 1;  // a tree of one group has nothing above level 0
+        for (int sg = 0; ok && sg < supers; ++sg) {
+          if (p.L >= 2) {
+            for (int i = 0; ok && i < p.F; ++i) drain_leaf(sA, i > 0);
+          }
+          for (int i = 0; ok && i < p.F; ++i) drain_leaf(s0, i > 0);
+          if (!ok) break;
+          int lvl = 1;
+          if (p.L >= 2) {
+#pragma unroll
+            for (int w = 0; w < NW; ++w) s0[w] = Pack16<T>::add(sA[w], s0[w]);  // the level-1 node
+            uint32_t gb = static_cast<uint32_t>(sg);
+            lvl = 2;
+            while (lvl < p.L && (gb & 1u)) {
+              uint32_t t[NW];
+              stack_load(lvl - 1, t);
+#pragma unroll
+              for (int w = 0; w < NW; ++w) s0[w] = Pack16<T>::add(t[w], s0[w]);
+              gb >>= 1;
+              ++lvl;
+            }
+          }
+          if (lvl < p.L) {
+            if (lvl == 2) staging_release();  // about to overwrite the slot the last tile of C was staged in
+            stack_store(lvl - 1, s0);
+          } else if (tma_c) {
+            stage_root(s0, tm, tn);
+          } else if (row < p.M) {
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+              const int col0 = tn * BN + h * C_::COLS_PER_WARP + c * CHUNK;
+              if (col0 >= p.N) continue;
+              if (vec_ok && col0 + CHUNK <= p.N) {
+                uint4* dst = reinterpret_cast<uint4*>(crow + col0);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  dst[j] = make_uint4(s0[c * 16 + 4 * j], s0[c * 16 + 4 * j + 1], s0[c * 16 + 4 * j + 2], s0[c * 16 + 4 * j + 3]);
+              } else {
+                uint16_t* dst = reinterpret_cast<uint16_t*>(crow + col0);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  if (col0 + 2 * j < p.N) dst[2 * j] = static_cast<uint16_t>(s0[c * 16 + j] & 0xFFFFu);
+                  if (col0 + 2 * j + 1 < p.N) dst[2 * j + 1] = static_cast<uint16_t>(s0[c * 16 + j] >> 16);
                 }
               }
             }
@@ -1226,18 +1326,33 @@ static Plan auto_plan(int M, int N, int L, int groups, int kblocks_total, int ma
   int ctas = sm_count(current_device());
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
   const int enough = ctas - ctas / 5;
-  // short K (at most 6 leaves of 256): the per-tile costs (pipeline refill, storing C) weigh more than the
-  // k-loop, and the 256x256 pair tile has half as many of them per flop (measured: K = 512 981 vs 752 TFLOP/s,
-  // K = 1536 1251 vs 1077; from K = 2048 on the 256x128 pair tile wins)
+  // Enough rows of C for every SM: one of the two CTA-pair tilings.  A 256x256 tile costs a little less than two
+  // 256x128 tiles -- a third less operand traffic per flop, UMMAs twice as long; measured at M = 8192, leaf 256:
+  // 1357 vs 1320 TFLOP/s at K = 4096, 1294 vs 1279 at K = 12288 -- and clearly less at short K, where the per-tile
+  // costs (pipeline refill, storing C) weigh more (K = 512: 981 vs 752, K = 1536: 1251 vs 1077).  What decides
+  // between them is the last, partial wave: whole waves of tiles x cost per tile.  The 256x256 tile needs the
+  // caller's scratch for the tree levels above the second.
   const bool short_k = kblocks_total <= 24;
-  const int order[6] = {short_k ? 4 : 2, short_k ? 2 : 4, 3, 1, 5, 6};
+  {
+    const int units = ctas / 2 > 0 ? ctas / 2 : 1;
+    Plan cand[2] = {make_plan(2, M, N, L, max_ctas), make_plan(4, M, N, L, max_ctas)};
+    double cost[2];
+    bool usable[2];
+    for (int i = 0; i < 2; ++i) {
+      const int tiles = cand[i].tiles_m * cand[i].tiles_n;
+      usable[i] = (cand[i].total_bytes() == 0 || (have_ws && cand[i].total_bytes() <= ws_bytes)) && 2 * tiles >= enough;
+      cost[i] = static_cast<double>((tiles + units - 1) / units) * (i == 0 ? 1.0 : (short_k ? 1.7 : 1.94));
+    }
+    if (usable[0] && usable[1]) return cost[1] < cost[0] ? cand[1] : cand[0];
+    if (usable[0]) return cand[0];
+    if (usable[1]) return cand[1];
+  }
+  const int order[6] = {2, 4, 3, 1, 5, 6};
   constexpr int kOrder = 6;
-  for (int i = 0; i < 4; ++i) {
-    if (!short_k && order[i] == 4) continue;  // long K: 256x256 only adds scratch need
+  for (int i = 2; i < 4; ++i) {
     Plan pl = make_plan(order[i], M, N, L, max_ctas);
     if (pl.total_bytes() > 0 && !(have_ws && pl.total_bytes() <= ws_bytes)) continue;
-    const Variant& pv = kVariants[order[i] - 1][pl.deep ? 1 : 0];
-    if (pl.tiles_m * pl.tiles_n * (pv.pair ? 2 : 1) >= enough) return pl;  // enough rows of C
+    if (pl.tiles_m * pl.tiles_n >= enough) return pl;  // enough rows of C
   }
   Plan best{};
   double best_cost = 0.0;

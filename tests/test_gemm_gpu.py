@@ -114,13 +114,15 @@ def test_very_deep_tree_scratch_rules():
 
 
 def test_entry_point_without_scratch_matches_the_ones_with_scratch():
-    """tbik_gemm (no scratch: the stack of the chosen tiling fits on chip), the 128x256 tiling (needs scratch for a
-    5-level tree) and tbik_gemm_ws at a decode-sized M (K-slabs, roots in the workspace) agree bitwise."""
+    """tbik_gemm (no scratch: it picks the 256x128 pair tiling, whose stack fits on chip), the schedule the automatic
+    choice prefers when it is given scratch (256x256 pair tiles), the 128x256 tiling (needs scratch for a 5-level tree)
+    and tbik_gemm_ws at a decode-sized M (K-slabs, roots in the workspace) agree bitwise."""
     from llm_reproducibility_b200 import _lib
     from llm_reproducibility_b200.tbik.tree_based_matmul import matmul_tp_persistent
     L = _lib.lib()
     M, K, N = 1000, 12288, 4096
-    assert L.tbik_gemm_workspace_bytes(M, N, K, 256) == 0         # 256x128 pair tiles: the whole stack in tensor memory
+    assert L.tbik_gemm_workspace_bytes(M, N, K, 256) > 0          # 256x256 pair tiles: upper stack levels in scratch
+    assert L.tbik_gemm_slabs_workspace_bytes(M, N, K, 256, 2, 1) == 0   # 256x128 pair tiles: the whole stack in tensor memory
     assert L.tbik_gemm_slabs_workspace_bytes(M, N, K, 256, 3, 1) > 0   # 128x256 tiles, 5-level tree: 3 levels go to scratch
     assert L.tbik_gemm_workspace_bytes(64, N, K, 256) > 0         # small M: room for the K-slab roots
     assert L.tbik_gemm_workspace_bytes(64, N, 256, 256) == 0      # one leaf: nothing to cut, no scratch
