@@ -56,7 +56,7 @@ HIDDEN = 4096
 LAYERS = (("o_proj", 4096, HIDDEN), ("down_proj", 12288, HIDDEN))  # (name, K, N)
 METRIC = "tp_invariant_row_split_gemm_plus_tree_allreduce_tflops"
 L2_BYTES = 126 * 1024 * 1024
-DOWN_PROJ_DRAM_BYTES = 1307.0e6  # ncu, M = 8192, 256x128 CTA-pair tiling, 8 row-tiles per group
+DOWN_PROJ_DRAM_BYTES = 1201.0e6  # ncu, M = 8192, 256x256 CTA-pair tiling (the automatic choice), 8 row-tiles per group
 
 
 def step_flops(M: int) -> float:
