@@ -83,9 +83,11 @@ size_t tbik_gemm_workspace_bytes(int M, int N, int64_t K, int leaf);
  * 16 KiB hold arrival counters that every completed call leaves at zero again, so the same buffer serves call
  * after call without further clearing; everything behind them may hold anything.  (If tbik_gemm_status ever
  * reports a kernel that gave up, clear the buffer again.)  The scratch serves the 256-column tilings (their
- * accumulators fill tensor memory, so the upper levels of the tree stack are kept in shared memory and, for
- * levels touched at most once every four leaves, in this buffer), trees deeper than the on-chip stack, and the
- * K-slab roots of decode-sized calls (below).  Same bits as tbik_gemm.
+ * accumulators fill tensor memory, so the upper levels of the tree stack are kept in registers and shared memory
+ * and, for levels touched at most once every four leaves, in this buffer), trees deeper than the on-chip stack,
+ * and the K-slab roots of decode-sized calls (below).  With scratch the automatic choice at large M is the 256x256
+ * CTA-pair tile (the fastest: a third less operand traffic per flop than 256x128); without it, 256x128.
+ * Same bits as tbik_gemm.
  * Replaces: the same reference functions as tbik_gemm. */
 int tbik_gemm_ws(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
                  int dtype, int leaf, int node_dtype, void* workspace, size_t workspace_bytes, tbik_stream_t stream);
