@@ -19,7 +19,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 RELATIVE_SOURCE = os.path.join("src", "tbik", "tree_based_matmul.py")
-DEFAULT_CHECKOUT = "/root/reference"
+DEFAULT_CHECKOUT = os.environ.get("TBIK_REFERENCE_CHECKOUT", "/root/reference")
 
 
 def build(checkout: str = DEFAULT_CHECKOUT) -> str | None:
