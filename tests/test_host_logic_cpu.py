@@ -82,6 +82,55 @@ def test_k_slab_plan_queries_need_no_gpu():
     assert need(M, 4090, K, 256, 1, 2) >= 2 * M * 4096 * 2                   # rows of the roots padded to 8 columns
 
 
+def test_automatic_plan_weighs_the_two_pair_tilings_by_whole_waves():
+    """With scratch the 256x256 CTA-pair tile (code 4) is taken unless the last partial wave makes 256x128 (code 2)
+    cheaper; without scratch only 256x128 can hold a tree of leaves of 256.  Host arithmetic (148 SMs assumed when
+    there is no device)."""
+    import ctypes
+    from llm_reproducibility_b200 import _lib
+    L = _lib.lib()
+    out = (ctypes.c_int * 4)()
+
+    def plan(M, N, K, ctas=0, ws=1 << 30):
+        assert L.tbik_gemm_plan(M, N, K, 256, ctas, ctypes.c_size_t(ws), out) == 0
+        return out[0], out[1], out[2]
+
+    assert plan(8192, 4096, 4096) == (4, 1, 148) and plan(8192, 4096, 12288) == (4, 1, 148)   # the benchmark step
+    assert plan(8192, 4096, 4096, ws=0)[0] == 2 and plan(8192, 4096, 12288, ws=0)[0] == 2     # no scratch
+    assert plan(8192, 4096, 512)[0] == 4                       # short K: fewer tiles to refill the pipeline for
+    assert plan(4096, 4096, 2048, ctas=116)[0] == 2            # 58 pairs: 9 waves of 256x128 against 5 of 256x256
+    t, s, _ = plan(16, 4096, 4096)                             # decode: a narrow tile and K-slabs
+    assert t in (5, 6) and s >= 2
+    assert L.tbik_gemm_workspace_bytes(8192, 4096, 4096, 256) > 0
+
+
+def test_fp32_node_leaf_rule_and_argument_checks():
+    """K_total / max_tp: exactly max_tp leaves, every level binary, a whole subtree per rank at every TP degree."""
+    import torch
+    from llm_reproducibility_b200 import _lib
+    from llm_reproducibility_b200.tbik.tree_based_matmul import _node_code, leaf_for_fp32_nodes, tree_shape
+    assert leaf_for_fp32_nodes(4096, 8) == 512 and leaf_for_fp32_nodes(12288, 8) == 1536
+    assert leaf_for_fp32_nodes(25600, 8) == 3200 and leaf_for_fp32_nodes(4096, 2) == 2048
+    for K, tp in ((4096, 8), (12288, 8), (25600, 8), (8192, 4)):
+        leaf = leaf_for_fp32_nodes(K, tp)
+        T, F, L = tree_shape(K, leaf)
+        assert T == tp and F <= 2 and L <= 3                       # fits the tensor-memory stack of the fast tilings
+        for deg in (1, 2, 4, 8):
+            if deg <= tp:
+                assert (K // deg) % leaf == 0                       # whole leaves per rank
+    with pytest.raises(ValueError):
+        leaf_for_fp32_nodes(4096, 3)
+    with pytest.raises(ValueError):
+        leaf_for_fp32_nodes(1000, 8)
+    a = torch.empty(1, dtype=torch.bfloat16)
+    assert _node_code(a, None, None) == _lib.NODE_INPUT and _node_code(a, torch.bfloat16, None) == _lib.NODE_INPUT
+    assert _node_code(a, torch.float32, None) == _lib.NODE_FP32
+    assert _node_code(a, torch.float32, torch.float32) == _lib.NODE_FP32_OUT_FP32
+    for bad in ((None, torch.float32), (torch.float64, None), (torch.float32, torch.float16)):
+        with pytest.raises(ValueError):
+            _node_code(a, *bad)
+
+
 def test_oracle_tree_shape_agrees_with_library():
     from llm_reproducibility_b200.tbik.tree_based_matmul import tree_shape as lib_shape
     from oracle.tbik_ref import tree_shape
