@@ -17,6 +17,8 @@ def lib() -> ctypes.CDLL:
         vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
         L.tbik_oracle_matmul.restype = i32
         L.tbik_oracle_matmul.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32]
+        L.tbik_oracle_matmul_fp32_nodes.restype = i32
+        L.tbik_oracle_matmul_fp32_nodes.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32]
         L.tbik_oracle_tree_allreduce.restype = i32
         L.tbik_oracle_tree_allreduce.argtypes = [ctypes.POINTER(vp), i32, vp, i64, i32]
         L.tbik_oracle_tree_shape.restype = i32
@@ -39,6 +41,19 @@ def matmul(A: torch.Tensor, B: torch.Tensor, leaf: int = 256) -> torch.Tensor:
     rc = lib().tbik_oracle_matmul(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, leaf, _DT[A.dtype])
     if rc != 0:
         raise ValueError(f"tbik_oracle_matmul failed with {rc}")
+    return C
+
+
+def matmul_fp32_nodes(A: torch.Tensor, B: torch.Tensor, leaf: int) -> torch.Tensor:
+    """The same tree with fp32 nodes and nothing rounded: the fp32 root, [M, N] float32."""
+    assert A.device.type == "cpu" and A.dtype in _DT and B.dtype == A.dtype
+    A, B = A.contiguous(), B.contiguous()
+    M, K = A.shape
+    N = B.shape[1]
+    C = torch.empty(M, N, dtype=torch.float32)
+    rc = lib().tbik_oracle_matmul_fp32_nodes(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, leaf, _DT[A.dtype])
+    if rc != 0:
+        raise ValueError(f"tbik_oracle_matmul_fp32_nodes failed with {rc}")
     return C
 
 

@@ -179,6 +179,54 @@ int tbik_oracle_matmul(const uint16_t* A, const uint16_t* B, uint16_t* C, int M,
   return failed ? -5 : 0;
 }
 
+/* The same tree with fp32 nodes (the CUDA library's fp32-node mode; the reference has no such mode): a leaf is the
+ * fp32 dot as it stands, every node is one fp32 add, nothing is rounded.  C32[M,N] receives the unrounded root; the
+ * caller rounds it once (tbik_oracle_down) when it wants a 16-bit result. */
+int tbik_oracle_matmul_fp32_nodes(const uint16_t* A, const uint16_t* B, float* C32, int M, int N, int K, int leaf,
+                                  int dtype) {
+  int T, F, L;
+  if (dtype != TBIK_ORACLE_BF16 && dtype != TBIK_ORACLE_FP16) return -3;
+  if (tbik_oracle_tree_shape(K, leaf, &T, &F, &L) != 0) return -2;
+  int failed = 0;
+#pragma omp parallel for schedule(static)
+  for (int m = 0; m < M; ++m) {
+    float* acc = (float*)malloc(sizeof(float) * (size_t)N);
+    float* stack = (float*)malloc(sizeof(float) * (size_t)N * (size_t)(L + 1));
+    if (!acc || !stack) {
+      failed = 1;
+      free(acc);
+      free(stack);
+      continue;
+    }
+    float* s0 = stack;
+    int c0 = 0;
+    unsigned g = 0;
+    for (int t = 0; t < T; ++t) {
+      for (int n = 0; n < N; ++n) acc[n] = 0.0f;
+      for (int k = t * leaf; k < (t + 1) * leaf; ++k) {
+        const float a = up(A[(size_t)m * K + k], dtype);
+        const uint16_t* b = B + (size_t)k * N;
+        for (int n = 0; n < N; ++n) acc[n] += a * up(b[n], dtype);
+      }
+      for (int n = 0; n < N; ++n) s0[n] = c0 > 0 ? s0[n] + acc[n] : acc[n];
+      if (++c0 < F) continue;
+      c0 = 0;
+      unsigned gb = g++;
+      int lvl = 1;
+      while (lvl < L && (gb & 1u)) {
+        const float* left = stack + (size_t)lvl * N;
+        for (int n = 0; n < N; ++n) s0[n] = left[n] + s0[n];
+        gb >>= 1;
+        ++lvl;
+      }
+      memcpy(lvl < L ? stack + (size_t)lvl * N : C32 + (size_t)m * N, s0, sizeof(float) * (size_t)N);
+    }
+    free(acc);
+    free(stack);
+  }
+  return failed ? -5 : 0;
+}
+
 /* out = ((p0 + p1) + (p2 + p3)) + ((p4 + p5) + (p6 + p7)), every add in the element type. */
 int tbik_oracle_tree_allreduce(const uint16_t* const* parts, int world, uint16_t* out, int64_t numel, int dtype) {
   if (world < 1 || world > 8 || (world & (world - 1)) != 0) return -2;

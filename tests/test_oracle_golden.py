@@ -156,3 +156,45 @@ def test_c_oracle_is_shard_invariant(dt, K, tps):
         assert torch.equal(bits(c_oracle.tree_allreduce(parts)), bits(full)), tp
     # batch invariance: a row computed alone has the bits it has inside the batch
     assert torch.equal(bits(c_oracle.matmul(A[2:3], B)), bits(full[2:3]))
+
+
+def _graded(M, K, N, leaf, dt, seed):
+    """Small integers, one power-of-two scale per leaf: leaves exact in fp32 whatever the order inside them, sums of
+    leaves not (the scales spread them over more than 24 bits)."""
+    g = torch.Generator().manual_seed(seed)
+    A = torch.randint(-15, 16, (M, K), generator=g).float()
+    B = torch.randint(-15, 16, (K, N), generator=g).float()
+    step = 5 if dt == torch.bfloat16 else 2
+    for i in range(K // leaf):
+        A[:, i * leaf:(i + 1) * leaf] *= 2.0 ** (-step * (i % 8))
+    return A.to(dt), B.to(dt)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,K,N,leaf", [(6, 4096, 24, 512), (5, 12288, 16, 1536), (4, 1536, 8, 256), (3, 2048, 8, 64),
+                                        (7, 512, 40, 512)])
+def test_fp32_node_oracles_agree_and_are_shard_invariant(dt, M, K, N, leaf):
+    """The fp32-node mode of the CUDA library (same tree, nothing rounded below the root; no such mode in the
+    reference) is checked against `tbik_matmul_ref(node_dtype=float32)`: here the C restatement, written
+    independently, gives the same bits, and K-shards combined by the rank-pair tree in fp32 give the unsplit root."""
+    from oracle import c_oracle
+    A, B = _graded(M, K, N, leaf, dt, seed=K + M)
+    py32 = tbik_matmul_ref(A, B, leaf, torch.float32, torch.float32)
+    c32 = c_oracle.matmul_fp32_nodes(A, B, leaf)
+    assert torch.equal(c32.view(torch.int32), py32.view(torch.int32))
+    assert torch.equal(bits(c_oracle.down(c32, dt)), bits(tbik_matmul_ref(A, B, leaf, torch.float32, dt)))
+    # the operands tell this mode from the reference's (rounded nodes) wherever there is more than one leaf
+    if K > leaf:
+        assert (bits(c_oracle.down(c32, dt)) != bits(c_oracle.matmul(A, B, leaf))).any()
+    T = K // leaf
+    for tp in (2, 4, 8):
+        if T % tp or (T & (T - 1)):
+            continue   # whole, aligned subtrees per rank need a power-of-two number of leaves
+        ks = K // tp
+        parts = [c_oracle.matmul_fp32_nodes(A[:, r * ks:(r + 1) * ks], B[r * ks:(r + 1) * ks], leaf) for r in range(tp)]
+        stride = 1
+        while stride < tp:
+            for i in range(0, tp, 2 * stride):
+                parts[i] = parts[i] + parts[i + stride]
+            stride *= 2
+        assert torch.equal(parts[0].view(torch.int32), c32.view(torch.int32)), tp
